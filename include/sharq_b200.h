@@ -1,0 +1,128 @@
+/*
+ * sharq_b200 - C ABI of the B200 (sm_100a) SharQ quantized-linear kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle
+ * (cudaStream_t passed as void*; NULL = the legacy default stream), enqueues its work
+ * on that stream and returns without synchronising.  Return value: 0 on success,
+ * non-zero on an argument or launch error; sharq_last_error() then returns a message
+ * (thread-local).  Unless stated otherwise an entry point allocates nothing and keeps
+ * no state: every buffer, including scratch, is provided by the caller.
+ *
+ * The entry points are what a binding of the reference's `sharq_ops` module would call:
+ * each comment names the reference op it stands behind (file:line in the reference
+ * project, kernels/src/bindings.cpp unless another file is named).
+ *
+ * Buffer formats (identical to the reference's):
+ *   payload     e2m1, two elements per byte (element 2i in the low nibble), row-major [rows, K/2]
+ *   A_comp      per 8 logical K the two kept pair-bytes, row-major [M, K/4]
+ *   E           per 8 logical K one nibble idx0 | idx1 << 2; layout [ceil(K/256)][ceil128(M)][16 B]
+ *   scales      UE4M3, blocked: 512-byte tiles of 128 rows x 4 scales
+ *               offset = (r/128)*(G/4)*512 + (g/4)*512 + (r%32)*16 + ((r/32)%4)*4 + g%4,
+ *               G = K/16 (dense) or K/32 (sparse main path); allocation (rows/128+1)*128*K/16
+ *   outputs     bf16 row-major [M, N]
+ */
+#ifndef SHARQ_B200_H_
+#define SHARQ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Library version (major*10000 + minor*100 + patch). */
+int sharq_version(void);
+
+/* Message of the last failing call on this thread ("" if none). */
+const char *sharq_last_error(void);
+
+/* get_sparse_nvfp4_buffer_sizes(M,N,K) -> (A_comp, E, SFA, SFB) bytes.  bindings.cpp:232-241 */
+int sharq_get_sparse_nvfp4_buffer_sizes(int m, int n, int k, int64_t out_bytes[4]);
+
+/* get_fused_sparse_residual_buffer_sizes(M,N,K) -> (A_comp, E, SFA_sparse, Q_res, SF_res) bytes.
+ * bindings.cpp:243-253 */
+int sharq_get_fused_sparse_residual_buffer_sizes(int m, int n, int k, int64_t out_bytes[5]);
+
+/* fused_sparse_residual_quantize_x(X, N): X is a pre-scaled bf16 [M,K], K % 128 == 0.
+ * Writes every byte of the five output buffers (sizes from the call above), padding
+ * included, so they need not be zero-initialised.  bindings.cpp:255-289 */
+int sharq_fused_sparse_residual_quantize_x(const void *x_bf16, int m, int n, int k, void *a_comp, void *e,
+                                           void *sfa_sparse, void *q_res, void *sf_res, void *stream);
+
+/* fused_sparse_residual_quantize_x_debug(X, N): dense sparse payload [M,K/2] instead of
+ * A_comp/E.  bindings.cpp:357-390 */
+int sharq_fused_sparse_residual_quantize_x_debug(const void *x_bf16, int m, int n, int k, void *q_sparse,
+                                                 void *sfa_sparse, void *q_res, void *sf_res, void *stream);
+
+/* Scratch bytes needed by the two scaled prepare calls below for M rows.  Layout:
+ * bytes [0,4) tensor absmax (float bits), bytes [256, 256+4*M) per-row inv_rms (float). */
+size_t sharq_prepare_workspace_bytes(int m);
+
+/* fused_rmsnorm_sparse_residual_quantize_x(X, rmsnorm_weight, eps, N): RMSNorm, tensor
+ * scale = clamp(amax/2688, 1e-9) and prepare in two launches (row statistics, prepare).
+ * K % 128 == 0 and K/32 <= 1024.  scale_out: one device float.  bindings.cpp:291-355 */
+int sharq_fused_rmsnorm_sparse_residual_quantize_x(const void *x_bf16, const void *rmsnorm_weight_bf16,
+                                                   float rmsnorm_eps, int m, int n, int k, void *workspace,
+                                                   size_t workspace_bytes, void *a_comp, void *e, void *sfa_sparse,
+                                                   void *q_res, void *sf_res, float *scale_out, void *stream);
+
+/* The non-RMSNorm activation path with its host-side passes folded in: computes
+ * scale = clamp(max|X|/2688, 1e-9), X' = bf16(X/scale) and the prepare of X'.  Equals
+ * global_nvfp4_scale + divide + fused_sparse_residual_quantize_x of the reference
+ * (model/quantize.py:179-183). */
+int sharq_scaled_sparse_residual_quantize_x(const void *x_bf16, int m, int n, int k, void *workspace,
+                                            size_t workspace_bytes, void *a_comp, void *e, void *sfa_sparse,
+                                            void *q_res, void *sf_res, float *scale_out, void *stream);
+
+/* quantize_w32_shared(W): bf16 [N,K] (already divided by the weight tensor scale),
+ * K % 32 == 0 -> QW [N,K/2], SFW_sparse (32-groups), SFW_dense (each scale duplicated
+ * into two 16-group slots).  bindings.cpp:392-417 */
+int sharq_quantize_w32_shared(const void *w_bf16, int n, int k, void *qw, void *sfw_sparse, void *sfw_dense,
+                              void *stream);
+
+/* duplicate_sfa32_to_sfa16(SFA_sparse, M, N, K).  bindings.cpp:419-437 */
+int sharq_duplicate_sfa32_to_sfa16(const void *sfa_sparse, int m, int n, int k, void *sfa_dense, void *stream);
+
+/* quantize_x_nvfp4(X) / quantize_w_nvfp4(W) (and reorder_quantize_x/w with the identity
+ * index and KE == 0): dense NVFP4, one scale per 16.  K % 16 == 0.  Only the used bytes
+ * of the scale buffer are written, as in the reference.  bindings.cpp:74-160 */
+int sharq_quantize_nvfp4(const void *x_bf16, int rows, int k, void *q, void *sf, void *stream);
+
+/* compress_sparse_a(A_q_dense, N): dense payload with at most two non-zero bytes per
+ * 4-byte chunk -> A_comp, E.  bindings.cpp:164-230 */
+int sharq_compress_sparse_a(const void *a_q_dense, int m, int n, int k, void *a_comp, void *e, void *stream);
+
+/* matmul / matmul_tensor_scale / matmul_accum / matmul_accum_tensor_scale:
+ * D = bf16(alpha * (A . B^T) + beta * C_in).  With alpha_dev (one device float) non-NULL
+ * the factor is alpha * (*alpha_dev) (the reference passes alpha = 1 then); c_in may be
+ * NULL when beta == 0.  K % 64 == 0.
+ * error_flag: one device int the kernel sets non-zero if an internal bounded wait ran
+ * out (never expected; the output is then undefined).  bindings.cpp:441-569 */
+int sharq_matmul(const void *a, const void *b, const void *sfa, const void *sfb, int m, int n, int k, float alpha,
+                 const float *alpha_dev, const void *c_in, float beta, void *d, int *error_flag, void *stream);
+
+/* sparse_matmul / sparse_matmul_tensor_scale: beta must be 0.  K % 128 == 0.
+ * bindings.cpp:571-701 */
+int sharq_sparse_matmul(const void *a_comp, const void *b, const void *e, const void *sfa, const void *sfb, int m,
+                        int n, int k, float alpha, const float *alpha_dev, float beta, void *d, int *error_flag,
+                        void *stream);
+
+/* The SharQ linear GEMM in one launch: D = bf16(alpha * (A_sparse + A_res) . W^T) (+ bias
+ * in bf16), the sparse main pass and the dense residual pass reading the same weight tile
+ * and accumulating into one tensor-memory tile.  Stands behind the two-launch composition
+ * of model/qLinearLayer.py:130-154 (+ bias add at :177-179) and is what the optional
+ * `sharq_linear_forward` op probed by benchmarks/vllm/sharq.py:206-213 runs. */
+int sharq_linear_gemm(const void *a_comp, const void *e, const void *sfa_sparse, const void *q_res,
+                      const void *sf_res, const void *qw, const void *sfw_sparse, const void *sfw_dense, int m, int n,
+                      int k, float alpha, const float *alpha_dev, const void *bias_bf16, void *d, int *error_flag,
+                      void *stream);
+
+/* Test/tuning hook: force the GEMM tile width (0 = automatic, 128 or 256).  Process-wide. */
+int sharq_set_gemm_tile_n(int tile_n);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* SHARQ_B200_H_ */

@@ -1,0 +1,235 @@
+// extern "C" boundary of the library (declared in include/sharq_b200.h): argument
+// checks with the reference's error conditions, then the launchers.
+#include "../../include/sharq_b200.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+#include "gemm.cuh"
+#include "prepare.cuh"
+#include "quant.cuh"
+
+namespace {
+
+thread_local char g_error[512] = "";
+int g_tile_n = 0;
+
+int fail(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return 1;
+}
+
+int check_cuda(cudaError_t err, const char *what) {
+  if (err == cudaSuccess) return 0;
+  return fail("%s: %s", what, cudaGetErrorString(err));
+}
+
+inline cudaStream_t as_stream(void *s) { return static_cast<cudaStream_t>(s); }
+
+#define SHARQ_REQUIRE(cond, ...) \
+  do {                           \
+    if (!(cond)) return fail(__VA_ARGS__); \
+  } while (0)
+
+}  // namespace
+
+extern "C" {
+
+int sharq_version(void) { return 100; }
+
+const char *sharq_last_error(void) { return g_error; }
+
+int sharq_get_sparse_nvfp4_buffer_sizes(int m, int n, int k, int64_t out[4]) {
+  SHARQ_REQUIRE(m > 0 && n > 0 && k > 0 && out, "M, N, K must be positive");
+  out[0] = (int64_t)sharq::a_comp_bytes(m, k);
+  out[1] = (int64_t)sharq::e_bytes(m, k);
+  out[2] = (int64_t)sharq::sf_alloc_bytes(m, k);
+  out[3] = (int64_t)sharq::sf_alloc_bytes(n, k);
+  return 0;
+}
+
+int sharq_get_fused_sparse_residual_buffer_sizes(int m, int n, int k, int64_t out[5]) {
+  SHARQ_REQUIRE(m > 0 && k > 0 && out, "M, K must be positive");
+  (void)n;
+  out[0] = (int64_t)sharq::a_comp_bytes(m, k);
+  out[1] = (int64_t)sharq::e_bytes(m, k);
+  out[2] = (int64_t)sharq::sf_alloc_bytes(m, k);
+  out[3] = (int64_t)m * (int64_t)(k / 2);
+  out[4] = (int64_t)sharq::sf_alloc_bytes(m, k);
+  return 0;
+}
+
+int sharq_fused_sparse_residual_quantize_x(const void *x, int m, int n, int k, void *a_comp, void *e, void *sfa_sparse,
+                                           void *q_res, void *sf_res, void *stream) {
+  (void)n;
+  SHARQ_REQUIRE(m > 0 && k > 0, "X must be shaped [M, K]");
+  SHARQ_REQUIRE(k % 128 == 0, "fused_sparse_residual_quantize_x currently requires K to be a multiple of 128, got %d", k);
+  SHARQ_REQUIRE(x && a_comp && e && sfa_sparse && q_res && sf_res, "null buffer");
+  return check_cuda(sharq::run_prepare(x, m, k, a_comp, e, nullptr, sfa_sparse, q_res, sf_res, as_stream(stream)),
+                    "fused_sparse_residual_quantize_x");
+}
+
+int sharq_fused_sparse_residual_quantize_x_debug(const void *x, int m, int n, int k, void *q_sparse, void *sfa_sparse,
+                                                 void *q_res, void *sf_res, void *stream) {
+  (void)n;
+  SHARQ_REQUIRE(m > 0 && k > 0, "X must be shaped [M, K]");
+  SHARQ_REQUIRE(k % 128 == 0,
+                "fused_sparse_residual_quantize_x_debug currently requires K to be a multiple of 128, got %d", k);
+  SHARQ_REQUIRE(x && q_sparse && sfa_sparse && q_res && sf_res, "null buffer");
+  return check_cuda(sharq::run_prepare(x, m, k, nullptr, nullptr, q_sparse, sfa_sparse, q_res, sf_res, as_stream(stream)),
+                    "fused_sparse_residual_quantize_x_debug");
+}
+
+size_t sharq_prepare_workspace_bytes(int m) { return sharq::prepare_workspace_bytes(m); }
+
+int sharq_fused_rmsnorm_sparse_residual_quantize_x(const void *x, const void *gamma, float eps, int m, int n, int k,
+                                                   void *workspace, size_t workspace_bytes, void *a_comp, void *e,
+                                                   void *sfa_sparse, void *q_res, void *sf_res, float *scale_out,
+                                                   void *stream) {
+  (void)n;
+  SHARQ_REQUIRE(m > 0 && k > 0, "X must be shaped [M, K]");
+  SHARQ_REQUIRE(k % 128 == 0,
+                "fused_rmsnorm_sparse_residual_quantize_x currently requires K to be a multiple of 128, got %d", k);
+  SHARQ_REQUIRE(k / 32 <= 1024, "fused_rmsnorm_sparse_residual_quantize_x requires K/32 <= 1024, got %d", k / 32);
+  SHARQ_REQUIRE(x && gamma && a_comp && e && sfa_sparse && q_res && sf_res, "null buffer");
+  SHARQ_REQUIRE(workspace && workspace_bytes >= sharq::prepare_workspace_bytes(m), "workspace too small: need %zu bytes",
+                sharq::prepare_workspace_bytes(m));
+  return check_cuda(sharq::run_scaled_prepare(x, gamma, eps, m, k, workspace, nullptr, a_comp, e, sfa_sparse, q_res,
+                                              sf_res, scale_out, as_stream(stream)),
+                    "fused_rmsnorm_sparse_residual_quantize_x");
+}
+
+int sharq_scaled_sparse_residual_quantize_x(const void *x, int m, int n, int k, void *workspace, size_t workspace_bytes,
+                                            void *a_comp, void *e, void *sfa_sparse, void *q_res, void *sf_res,
+                                            float *scale_out, void *stream) {
+  (void)n;
+  SHARQ_REQUIRE(m > 0 && k > 0, "X must be shaped [M, K]");
+  SHARQ_REQUIRE(k % 128 == 0, "scaled_sparse_residual_quantize_x requires K to be a multiple of 128, got %d", k);
+  SHARQ_REQUIRE(x && a_comp && e && sfa_sparse && q_res && sf_res, "null buffer");
+  SHARQ_REQUIRE(workspace && workspace_bytes >= 256, "workspace too small: need 256 bytes");
+  return check_cuda(sharq::run_scaled_prepare(x, nullptr, 0.0f, m, k, workspace, nullptr, a_comp, e, sfa_sparse, q_res,
+                                              sf_res, scale_out, as_stream(stream)),
+                    "scaled_sparse_residual_quantize_x");
+}
+
+int sharq_quantize_w32_shared(const void *w, int n, int k, void *qw, void *sfw_sparse, void *sfw_dense, void *stream) {
+  SHARQ_REQUIRE(n > 0 && k > 0, "W must be shaped [N, K]");
+  SHARQ_REQUIRE(k % 32 == 0, "quantize_w32_shared requires K to be a multiple of 32, got %d", k);
+  SHARQ_REQUIRE(k / 32 <= 1024, "run_quantize_w32_bf16_nvfp4_shared requires hidden_dim / 32 <= 1024");
+  SHARQ_REQUIRE(w && qw && sfw_sparse && sfw_dense, "null buffer");
+  return check_cuda(sharq::run_quantize_w32_shared(w, n, k, qw, sfw_sparse, sfw_dense, as_stream(stream)),
+                    "quantize_w32_shared");
+}
+
+int sharq_duplicate_sfa32_to_sfa16(const void *sfa_sparse, int m, int n, int k, void *sfa_dense, void *stream) {
+  (void)n;
+  SHARQ_REQUIRE(m > 0 && k > 0, "M, K must be positive");
+  SHARQ_REQUIRE(k % 32 == 0, "run_duplicate_sfa32_to_sfa16 requires hidden_dim to be a multiple of 32");
+  SHARQ_REQUIRE(k / 32 <= 1024, "run_duplicate_sfa32_to_sfa16 requires hidden_dim / 32 <= 1024");
+  SHARQ_REQUIRE(sfa_sparse && sfa_dense, "null buffer");
+  return check_cuda(sharq::run_duplicate_sf32_to_sf16(sfa_sparse, m, k, sfa_dense, as_stream(stream)),
+                    "duplicate_sfa32_to_sfa16");
+}
+
+int sharq_quantize_nvfp4(const void *x, int rows, int k, void *q, void *sf, void *stream) {
+  SHARQ_REQUIRE(rows > 0 && k > 0, "input must be shaped [rows, K]");
+  SHARQ_REQUIRE(k % 16 == 0, "Unsupported hidden size %d: K must be a multiple of 16", k);
+  SHARQ_REQUIRE(x && q && sf, "null buffer");
+  return check_cuda(sharq::run_quantize_dense_nvfp4(x, rows, k, q, sf, as_stream(stream)), "quantize_nvfp4");
+}
+
+int sharq_compress_sparse_a(const void *a_q_dense, int m, int n, int k, void *a_comp, void *e, void *stream) {
+  (void)n;
+  SHARQ_REQUIRE(m > 0 && k > 0, "A_q_dense must be shaped [M, K/2]");
+  SHARQ_REQUIRE(k % 32 == 0, "compress_sparse_a requires K to be a multiple of 32, got %d", k);
+  SHARQ_REQUIRE(a_q_dense && a_comp && e, "null buffer");
+  return check_cuda(sharq::run_compress_sparse_a(a_q_dense, m, k, a_comp, e, as_stream(stream)), "compress_sparse_a");
+}
+
+int sharq_set_gemm_tile_n(int tile_n) {
+  SHARQ_REQUIRE(tile_n == 0 || tile_n == 128 || tile_n == 256, "tile_n must be 0, 128 or 256");
+  g_tile_n = tile_n;
+  return 0;
+}
+
+int sharq_matmul(const void *a, const void *b, const void *sfa, const void *sfb, int m, int n, int k, float alpha,
+                 const float *alpha_dev, const void *c_in, float beta, void *d, int *error_flag, void *stream) {
+  SHARQ_REQUIRE(m > 0 && n > 0 && k > 0, "M, N, K must be positive");
+  SHARQ_REQUIRE(k % 64 == 0, "matmul requires K to be a multiple of 64, got %d", k);
+  SHARQ_REQUIRE(a && b && sfa && sfb && d && error_flag, "null buffer");
+  SHARQ_REQUIRE(beta == 0.0f || c_in != nullptr, "C_in must be given when beta != 0");
+  sharq::GemmArgs g;
+  g.a_dense = a;
+  g.sfa_dense = sfa;
+  g.b = b;
+  g.sfb_dense = sfb;
+  g.c_in = c_in;
+  g.d = d;
+  g.alpha = alpha;
+  g.alpha_ptr = alpha_dev;
+  g.beta = beta;
+  g.m = m;
+  g.n = n;
+  g.k = k;
+  g.tile_n = g_tile_n;
+  g.error_flag = error_flag;
+  return check_cuda(sharq::run_gemm(g, as_stream(stream)), "matmul");
+}
+
+int sharq_sparse_matmul(const void *a_comp, const void *b, const void *e, const void *sfa, const void *sfb, int m, int n,
+                        int k, float alpha, const float *alpha_dev, float beta, void *d, int *error_flag, void *stream) {
+  SHARQ_REQUIRE(m > 0 && n > 0 && k > 0, "M, N, K must be positive");
+  SHARQ_REQUIRE(beta == 0.0f, "sparse_matmul currently requires beta == 0");
+  SHARQ_REQUIRE(k % 128 == 0, "sparse_matmul requires K to be a multiple of 128, got %d", k);
+  SHARQ_REQUIRE(a_comp && b && e && sfa && sfb && d && error_flag, "null buffer");
+  sharq::GemmArgs g;
+  g.a_comp = a_comp;
+  g.e = e;
+  g.sfa_sparse = sfa;
+  g.b = b;
+  g.sfb_sparse = sfb;
+  g.d = d;
+  g.alpha = alpha;
+  g.alpha_ptr = alpha_dev;
+  g.m = m;
+  g.n = n;
+  g.k = k;
+  g.tile_n = g_tile_n;
+  g.error_flag = error_flag;
+  return check_cuda(sharq::run_gemm(g, as_stream(stream)), "sparse_matmul");
+}
+
+int sharq_linear_gemm(const void *a_comp, const void *e, const void *sfa_sparse, const void *q_res, const void *sf_res,
+                      const void *qw, const void *sfw_sparse, const void *sfw_dense, int m, int n, int k, float alpha,
+                      const float *alpha_dev, const void *bias, void *d, int *error_flag, void *stream) {
+  SHARQ_REQUIRE(m > 0 && n > 0 && k > 0, "M, N, K must be positive");
+  SHARQ_REQUIRE(k % 128 == 0, "linear_gemm requires K to be a multiple of 128, got %d", k);
+  SHARQ_REQUIRE(a_comp && e && sfa_sparse && q_res && sf_res && qw && sfw_sparse && sfw_dense && d && error_flag,
+                "null buffer");
+  sharq::GemmArgs g;
+  g.a_comp = a_comp;
+  g.e = e;
+  g.sfa_sparse = sfa_sparse;
+  g.a_dense = q_res;
+  g.sfa_dense = sf_res;
+  g.b = qw;
+  g.sfb_sparse = sfw_sparse;
+  g.sfb_dense = sfw_dense;
+  g.bias = bias;
+  g.d = d;
+  g.alpha = alpha;
+  g.alpha_ptr = alpha_dev;
+  g.m = m;
+  g.n = n;
+  g.k = k;
+  g.tile_n = g_tile_n;
+  g.error_flag = error_flag;
+  return check_cuda(sharq::run_gemm(g, as_stream(stream)), "linear_gemm");
+}
+
+}  // extern "C"

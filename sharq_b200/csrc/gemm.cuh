@@ -1,0 +1,33 @@
+// Host launcher of the block-scaled FP4 GEMMs (gemm.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+namespace sharq {
+
+struct GemmArgs {
+  // Sparse main path operand (all three null => dense-only GEMM).
+  const void *a_comp = nullptr;      // [m, k/4] compressed e2m1 pairs
+  const void *e = nullptr;           // metadata, [k/256][ceil128(m)][16 B]
+  const void *sfa_sparse = nullptr;  // UE4M3 per 32 along K, blocked layout
+  // Dense operand (null => sparse-only GEMM).
+  const void *a_dense = nullptr;    // [m, k/2] e2m1
+  const void *sfa_dense = nullptr;  // UE4M3 per 16 along K, blocked layout
+  // Weight: one payload, two views of its scales.
+  const void *b = nullptr;           // [n, k/2] e2m1
+  const void *sfb_sparse = nullptr;  // per 32 (used by the sparse pass)
+  const void *sfb_dense = nullptr;   // per 16 (used by the dense pass)
+  // Epilogue: d = bf16(alpha * acc + beta * c_in), then (+ bias) in bf16.
+  const void *c_in = nullptr;  // [m, n] bf16, optional
+  const void *bias = nullptr;  // [n] bf16, optional
+  void *d = nullptr;           // [m, n] bf16
+  const float *alpha_ptr = nullptr;  // device scalar; when non-null the factor is alpha * (*alpha_ptr)
+  float alpha = 1.0f;
+  float beta = 0.0f;
+  int m = 0, n = 0, k = 0;
+  int tile_n = 0;             // 0 = choose, else 128 or 256
+  int *error_flag = nullptr;  // device int, set non-zero when a bounded wait ran out
+};
+
+cudaError_t run_gemm(const GemmArgs &args, cudaStream_t stream);
+
+}  // namespace sharq

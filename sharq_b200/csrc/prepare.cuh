@@ -1,0 +1,24 @@
+// Host launchers of the activation prepare kernels (prepare.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+namespace sharq {
+
+// Bytes of scratch the scaled / RMSNorm-fused prepare needs for M rows:
+// [0,4) tensor absmax bits, [256, 256 + 4*M) per-row inv_rms.
+size_t prepare_workspace_bytes(int m);
+
+// Prepare of an already scaled bf16 activation [m,k].  With q_sparse_dense != nullptr
+// the debug variant runs (dense sparse payload instead of a_comp/e).
+cudaError_t run_prepare(const void *x, int m, int k, void *a_comp, void *e, void *q_sparse_dense,
+                        void *sfa_sparse, void *q_res, void *sf_res, cudaStream_t stream);
+
+// Row statistics + prepare with the tensor scale (and RMSNorm when gamma != nullptr)
+// applied inline.  inv_rms_external (optional) receives the per-row inv_rms instead of
+// the workspace slot.
+cudaError_t run_scaled_prepare(const void *x, const void *gamma, float eps, int m, int k, void *workspace,
+                               float *inv_rms_external, void *a_comp, void *e, void *sfa_sparse, void *q_res,
+                               void *sf_res, float *scale_out, cudaStream_t stream);
+
+}  // namespace sharq

@@ -1,0 +1,386 @@
+"""The reference's `sharq_ops` operator set on top of the sm_100a C ABI.
+
+Every function has the name, argument meaning, return shapes/dtypes and error
+conditions of the op with that name in the reference's extension
+(kernels/src/bindings.cpp:705-766 of the reference project): inputs are borrowed
+contiguous CUDA tensors, outputs are new tensors from the torch caching allocator,
+nothing is mutated, argument errors raise RuntimeError.  Kernels are enqueued on
+torch's current stream of the input's device and the call returns without
+synchronising.  PyTorch is used only for memory and streams; all arithmetic happens in
+libsharq_b200.so.  There is no fallback path: a missing library raises ImportError.
+
+Extra ops that the reference does not have (all optional for a drop-in):
+  sharq_linear_forward           the op name the reference's vLLM plugin probes for
+  sharq_linear_gemm              fused sparse+residual GEMM on a prepared activation
+  scaled_sparse_residual_quantize_x   prepare with the host-side amax/divide folded in
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+_ERROR_FLAGS: dict[int, torch.Tensor] = {}
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(device: torch.device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _error_flag(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    flag = _ERROR_FLAGS.get(idx)
+    if flag is None:
+        flag = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _ERROR_FLAGS[idx] = flag
+    return flag
+
+
+def check_device_errors(device=None) -> None:
+    """Synchronising check of the GEMM kernels' bounded-wait error flag."""
+    for idx, flag in list(_ERROR_FLAGS.items()):
+        if device is not None and torch.device(device).index not in (None, idx):
+            continue
+        code = int(flag.item())
+        if code != 0:
+            flag.zero_()
+            raise RuntimeError(f"sharq_b200 GEMM kernel reported a timed-out wait (code {code}) on cuda:{idx}")
+
+
+def _u8(n: int, device) -> torch.Tensor:
+    return torch.empty(int(n), dtype=torch.uint8, device=device)
+
+
+def _sf_bytes(rows: int, k: int) -> int:
+    return (rows // 128 + 1) * 128 * k // 16
+
+
+# --------------------------------------------------------------------------- sizes
+
+def get_sparse_nvfp4_buffer_sizes(M: int, N: int, K: int) -> Tuple[int, int, int, int]:
+    out = (ctypes.c_int64 * 4)()
+    _lib.check(_lib.lib().sharq_get_sparse_nvfp4_buffer_sizes(M, N, K, out))
+    return tuple(int(v) for v in out)
+
+
+def get_fused_sparse_residual_buffer_sizes(M: int, N: int, K: int) -> Tuple[int, int, int, int, int]:
+    out = (ctypes.c_int64 * 5)()
+    _lib.check(_lib.lib().sharq_get_fused_sparse_residual_buffer_sizes(M, N, K, out))
+    return tuple(int(v) for v in out)
+
+
+# --------------------------------------------------------------------------- activation prepare
+
+def _check_x(X: torch.Tensor, name: str = "X") -> Tuple[int, int]:
+    _check(X.is_cuda, f"{name} must be a CUDA tensor")
+    _check(X.is_contiguous(), f"{name} must be contiguous")
+    _check(X.dtype == torch.bfloat16, f"{name} must be torch.bfloat16")
+    _check(X.dim() == 2, f"{name} must be shaped [M, K]")
+    return int(X.shape[0]), int(X.shape[1])
+
+
+def fused_sparse_residual_quantize_x(X: torch.Tensor, N: int):
+    """-> (A_comp, E, SFA_sparse, Q_res [M,K/2], SF_res)."""
+    M, K = _check_x(X)
+    _check(K % 128 == 0, f"fused_sparse_residual_quantize_x currently requires K to be a multiple of 128, got {K}")
+    sa, se, ssf, _, ssr = get_fused_sparse_residual_buffer_sizes(M, N, K)
+    dev = X.device
+    A_comp, E, SFA, SF_res = _u8(sa, dev), _u8(se, dev), _u8(ssf, dev), _u8(ssr, dev)
+    Q_res = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().sharq_fused_sparse_residual_quantize_x(
+            _ptr(X), M, N, K, _ptr(A_comp), _ptr(E), _ptr(SFA), _ptr(Q_res), _ptr(SF_res), _stream(dev)))
+    return A_comp, E, SFA, Q_res, SF_res
+
+
+def fused_sparse_residual_quantize_x_debug(X: torch.Tensor, N: int):
+    """-> (Q_sparse dense payload [M,K/2], SFA_sparse, Q_res, SF_res)."""
+    M, K = _check_x(X)
+    _check(K % 128 == 0,
+           f"fused_sparse_residual_quantize_x_debug currently requires K to be a multiple of 128, got {K}")
+    dev = X.device
+    Q_sparse = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
+    Q_res = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
+    SFA, SF_res = _u8(_sf_bytes(M, K), dev), _u8(_sf_bytes(M, K), dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().sharq_fused_sparse_residual_quantize_x_debug(
+            _ptr(X), M, N, K, _ptr(Q_sparse), _ptr(SFA), _ptr(Q_res), _ptr(SF_res), _stream(dev)))
+    return Q_sparse, SFA, Q_res, SF_res
+
+
+def _scaled_prepare(X, gamma, eps, N, return_workspace):
+    M, K = int(X.shape[0]), int(X.shape[1])
+    sa, se, ssf, _, ssr = get_fused_sparse_residual_buffer_sizes(M, N, K)
+    dev = X.device
+    A_comp, E, SFA, SF_res = _u8(sa, dev), _u8(se, dev), _u8(ssf, dev), _u8(ssr, dev)
+    Q_res = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
+    scale = torch.empty((), dtype=torch.float32, device=dev)
+    ws_bytes = int(_lib.lib().sharq_prepare_workspace_bytes(M))
+    ws = _u8(ws_bytes, dev)
+    with torch.cuda.device(dev):
+        if gamma is not None:
+            _lib.check(_lib.lib().sharq_fused_rmsnorm_sparse_residual_quantize_x(
+                _ptr(X), _ptr(gamma), float(eps), M, N, K, _ptr(ws), ws_bytes, _ptr(A_comp), _ptr(E), _ptr(SFA),
+                _ptr(Q_res), _ptr(SF_res), _ptr(scale), _stream(dev)))
+        else:
+            _lib.check(_lib.lib().sharq_scaled_sparse_residual_quantize_x(
+                _ptr(X), M, N, K, _ptr(ws), ws_bytes, _ptr(A_comp), _ptr(E), _ptr(SFA), _ptr(Q_res), _ptr(SF_res),
+                _ptr(scale), _stream(dev)))
+    if return_workspace:
+        return A_comp, E, SFA, Q_res, SF_res, scale, ws
+    return A_comp, E, SFA, Q_res, SF_res, scale
+
+
+def fused_rmsnorm_sparse_residual_quantize_x(X: torch.Tensor, rmsnorm_weight: torch.Tensor, rmsnorm_eps: float,
+                                             N: int, return_workspace: bool = False):
+    """-> (A_comp, E, SFA_sparse, Q_res, SF_res, scale [0-dim float32]).
+
+    With return_workspace=True the scratch buffer is appended (bytes [256, 256+4M) hold
+    the per-row inv_rms as float32)."""
+    M, K = _check_x(X)
+    w = rmsnorm_weight
+    _check(w.is_cuda, "rmsnorm_weight must be a CUDA tensor")
+    _check(w.is_contiguous(), "rmsnorm_weight must be contiguous")
+    _check(w.dtype == torch.bfloat16, "rmsnorm_weight must be torch.bfloat16")
+    _check(w.dim() == 1, "rmsnorm_weight must be shaped [K]")
+    _check(w.device == X.device, "rmsnorm_weight must be on the same device as X")
+    _check(w.shape[0] == K, f"rmsnorm_weight size mismatch: expected {K}, got {w.shape[0]}")
+    _check(K % 128 == 0,
+           f"fused_rmsnorm_sparse_residual_quantize_x currently requires K to be a multiple of 128, got {K}")
+    _check(K // 32 <= 1024, f"fused_rmsnorm_sparse_residual_quantize_x requires K/32 <= 1024, got {K // 32}")
+    return _scaled_prepare(X, w, rmsnorm_eps, N, return_workspace)
+
+
+def scaled_sparse_residual_quantize_x(X: torch.Tensor, N: int):
+    """Unscaled bf16 X -> (A_comp, E, SFA_sparse, Q_res, SF_res, scale): tensor scale,
+    division and prepare in two launches (extra op, not in the reference)."""
+    M, K = _check_x(X)
+    _check(K % 128 == 0, f"scaled_sparse_residual_quantize_x requires K to be a multiple of 128, got {K}")
+    return _scaled_prepare(X, None, 0.0, N, False)
+
+
+# --------------------------------------------------------------------------- weights / dense quant
+
+def quantize_w32_shared(W: torch.Tensor):
+    """-> (QW [N,K/2], SFW_sparse, SFW_dense)."""
+    _check(W.is_cuda, "W must be a CUDA tensor")
+    _check(W.is_contiguous(), "W must be contiguous")
+    _check(W.dtype == torch.bfloat16, "W must be torch.bfloat16")
+    _check(W.dim() == 2, "W must be shaped [N, K]")
+    N, K = int(W.shape[0]), int(W.shape[1])
+    _check(K % 32 == 0, f"quantize_w32_shared requires K to be a multiple of 32, got {K}")
+    dev = W.device
+    QW = torch.empty((N, K // 2), dtype=torch.uint8, device=dev)
+    SFS, SFD = _u8(_sf_bytes(N, K), dev), _u8(_sf_bytes(N, K), dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().sharq_quantize_w32_shared(_ptr(W), N, K, _ptr(QW), _ptr(SFS), _ptr(SFD), _stream(dev)))
+    return QW, SFS, SFD
+
+
+def duplicate_sfa32_to_sfa16(SFA_sparse: torch.Tensor, M: int, N: int, K: int) -> torch.Tensor:
+    _check(SFA_sparse.is_cuda, "SFA_sparse must be a CUDA tensor")
+    _check(SFA_sparse.is_contiguous(), "SFA_sparse must be contiguous")
+    _check(SFA_sparse.dtype == torch.uint8, "SFA_sparse must be torch.uint8")
+    dev = SFA_sparse.device
+    out = _u8(_sf_bytes(M, K), dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().sharq_duplicate_sfa32_to_sfa16(_ptr(SFA_sparse), M, N, K, _ptr(out), _stream(dev)))
+    return out
+
+
+def _quantize_nvfp4(X: torch.Tensor, what: str):
+    rows, K = int(X.shape[0]), int(X.shape[1])
+    if K % 16 != 0:
+        raise RuntimeError(f"Unsupported hidden size in {what}")
+    dev = X.device
+    Q = torch.empty((rows, K // 2), dtype=torch.uint8, device=dev)
+    SF = _u8(_sf_bytes(rows, K), dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().sharq_quantize_nvfp4(_ptr(X.contiguous()), rows, K, _ptr(Q), _ptr(SF), _stream(dev)))
+    return Q, SF
+
+
+def quantize_x_nvfp4(X: torch.Tensor):
+    """Dense NVFP4 activation quantisation -> (QX [M,K/2], SFX)."""
+    return _quantize_nvfp4(X, "reorder_quantize_x")
+
+
+def quantize_w_nvfp4(W: torch.Tensor):
+    """Dense NVFP4 weight quantisation -> (QW [N,K/2], SFW)."""
+    return _quantize_nvfp4(W, "reorder_quantize_w")
+
+
+def _check_identity(reorder_index: torch.Tensor, K: int, KE: int) -> None:
+    _check(int(KE) == 0, "sharq_b200 supports the deprecated reorder ops only with KE == 0")
+    _check(reorder_index.numel() == K, "reorder_index must have K entries")
+    ident = torch.arange(K, dtype=reorder_index.dtype, device=reorder_index.device)
+    _check(bool(torch.equal(reorder_index, ident)), "sharq_b200 supports the deprecated reorder ops only with the identity index")
+
+
+def reorder_quantize_x(X: torch.Tensor, reorder_index: torch.Tensor, KE: int):
+    """Deprecated alias of quantize_x_nvfp4 (identity index, KE == 0 only)."""
+    _check_identity(reorder_index, int(X.shape[1]), KE)
+    return quantize_x_nvfp4(X)
+
+
+def reorder_quantize_w(W: torch.Tensor, reorder_index: torch.Tensor, KE: int):
+    """Deprecated alias of quantize_w_nvfp4 (identity index, KE == 0 only)."""
+    _check_identity(reorder_index, int(W.shape[1]), KE)
+    return quantize_w_nvfp4(W)
+
+
+def compress_sparse_a(A_q_dense: torch.Tensor, N: int):
+    """Dense payload with <= 2 non-zero bytes per 4 -> (A_comp, E)."""
+    _check(A_q_dense.is_cuda, "A_q_dense must be a CUDA tensor")
+    _check(A_q_dense.is_contiguous(), "A_q_dense must be contiguous")
+    _check(A_q_dense.dtype == torch.uint8, "A_q_dense must be torch.uint8")
+    _check(A_q_dense.dim() == 2, "A_q_dense must be shaped [M, K/2]")
+    M, K = int(A_q_dense.shape[0]), int(A_q_dense.shape[1]) * 2
+    sa, se, _, _ = get_sparse_nvfp4_buffer_sizes(M, N, K)
+    dev = A_q_dense.device
+    A_comp, E = _u8(sa, dev), _u8(se, dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().sharq_compress_sparse_a(_ptr(A_q_dense), M, N, K, _ptr(A_comp), _ptr(E), _stream(dev)))
+    return A_comp, E
+
+
+# --------------------------------------------------------------------------- GEMMs
+
+def _scale_ptr(scale: torch.Tensor, reference: torch.Tensor, name: str):
+    _check(scale.is_cuda, f"{name} must be a CUDA tensor")
+    _check(scale.is_contiguous(), f"{name} must be contiguous")
+    _check(scale.dtype == torch.float32, f"{name} must be torch.float32")
+    _check(scale.numel() == 1, f"{name} must contain exactly one element")
+    _check(scale.device == reference.device, f"{name} must be on the same device as the inputs")
+    return _ptr(scale)
+
+
+def _dense_gemm(A, B, SFA, SFB, alpha, alpha_t, C_in, beta):
+    M, N, K = int(A.shape[0]), int(B.shape[0]), int(A.shape[1]) * 2
+    dev = A.device
+    D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().sharq_matmul(
+            _ptr(A), _ptr(B), _ptr(SFA), _ptr(SFB), M, N, K, float(alpha),
+            None if alpha_t is None else _scale_ptr(alpha_t, A, "scale"), _ptr(C_in), float(beta), _ptr(D),
+            _ptr(_error_flag(dev)), _stream(dev)))
+    return D
+
+
+def _check_c_in(C_in, A, M, N):
+    _check(C_in.is_cuda, "C_in must be a CUDA tensor")
+    _check(C_in.is_contiguous(), "C_in must be contiguous")
+    _check(C_in.dtype == torch.bfloat16, "C_in must be torch.bfloat16")
+    _check(C_in.dim() == 2, "C_in must be shaped [M, N]")
+    _check(C_in.shape[0] == M and C_in.shape[1] == N,
+           f"C_in shape mismatch: expected [{M}, {N}] got [{C_in.shape[0]}, {C_in.shape[1]}]")
+    _check(C_in.device == A.device, "C_in must be on the same device as A")
+
+
+def matmul(A, B, SFA, SFB, scale: float):
+    """Dense NVFP4 GEMM -> bf16 [M,N] = scale * A.B^T."""
+    return _dense_gemm(A, B, SFA, SFB, scale, None, None, 0.0)
+
+
+def matmul_tensor_scale(A, B, SFA, SFB, scale: torch.Tensor):
+    return _dense_gemm(A, B, SFA, SFB, 1.0, scale, None, 0.0)
+
+
+def matmul_accum(A, B, SFA, SFB, scale: float, C_in, beta: float = 1.0):
+    """-> new bf16 [M,N] = scale * A.B^T + beta * C_in."""
+    _check_c_in(C_in, A, int(A.shape[0]), int(B.shape[0]))
+    return _dense_gemm(A, B, SFA, SFB, scale, None, C_in, beta)
+
+
+def matmul_accum_tensor_scale(A, B, SFA, SFB, scale: torch.Tensor, C_in, beta: float = 1.0):
+    _check_c_in(C_in, A, int(A.shape[0]), int(B.shape[0]))
+    return _dense_gemm(A, B, SFA, SFB, 1.0, scale, C_in, beta)
+
+
+def _sparse_gemm(name, A_comp, B, E, SFA, SFB, M, N, K, alpha, alpha_t, beta):
+    _check(M > 0 and N > 0 and K > 0, "M, N, K must be positive")
+    _check(beta == 0.0, f"{name} currently requires beta == 0")
+    ts = (A_comp, B, E, SFA, SFB)
+    _check(all(t.is_cuda for t in ts), f"{name} inputs must be CUDA tensors")
+    _check(all(t.is_contiguous() for t in ts), f"{name} inputs must be contiguous")
+    for t, nm in zip(ts, ("A_comp", "B", "E", "SFA", "SFB")):
+        _check(t.dtype == torch.uint8, f"{nm} must be torch.uint8")
+    _check(all(t.device == A_comp.device for t in ts), f"{name} inputs must be on the same device")
+    ea, ee, esfa, esfb = get_sparse_nvfp4_buffer_sizes(M, N, K)
+    _check(A_comp.numel() == ea, f"A_comp.numel() mismatch: expected {ea}, got {A_comp.numel()}")
+    _check(E.numel() == ee, f"E.numel() mismatch: expected {ee}, got {E.numel()}")
+    _check(SFA.numel() == esfa, f"SFA.numel() mismatch: expected {esfa}, got {SFA.numel()}")
+    _check(SFB.numel() == esfb, f"SFB.numel() mismatch: expected {esfb}, got {SFB.numel()}")
+    _check(B.dim() == 2, "B must be a 2D tensor shaped [N, K/2]")
+    _check(B.shape[0] == N, f"B.size(0) mismatch: expected {N}, got {B.shape[0]}")
+    _check(B.shape[1] == K // 2, f"B.size(1) mismatch: expected {K // 2}, got {B.shape[1]}")
+    dev = A_comp.device
+    D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().sharq_sparse_matmul(
+            _ptr(A_comp), _ptr(B), _ptr(E), _ptr(SFA), _ptr(SFB), M, N, K, float(alpha),
+            None if alpha_t is None else _scale_ptr(alpha_t, A_comp, "alpha"), float(beta), _ptr(D),
+            _ptr(_error_flag(dev)), _stream(dev)))
+    return D
+
+
+def sparse_matmul(A_comp, B, E, SFA, SFB, M: int, N: int, K: int, alpha: float = 1.0, beta: float = 0.0):
+    """Sparse NVFP4 GEMM on precompressed A -> bf16 [M,N]."""
+    return _sparse_gemm("sparse_matmul", A_comp, B, E, SFA, SFB, M, N, K, alpha, None, beta)
+
+
+def sparse_matmul_tensor_scale(A_comp, B, E, SFA, SFB, M: int, N: int, K: int, alpha: torch.Tensor,
+                               beta: float = 0.0):
+    return _sparse_gemm("sparse_matmul_tensor_scale", A_comp, B, E, SFA, SFB, M, N, K, 1.0, alpha, beta)
+
+
+def sharq_linear_gemm(A_comp, E, SFA_sparse, Q_res, SF_res, QW, SFW_sparse, SFW_dense, alpha,
+                      bias: Optional[torch.Tensor] = None, alpha_host: float = 1.0) -> torch.Tensor:
+    """Fused sparse-main + dense-residual GEMM on a prepared activation (one launch).
+    alpha: python float or 1-element CUDA float32 tensor; the factor applied is
+    alpha * alpha_host."""
+    M, K = int(Q_res.shape[0]), int(Q_res.shape[1]) * 2
+    N = int(QW.shape[0])
+    dev = Q_res.device
+    if bias is not None:
+        _check(bias.is_cuda and bias.dtype == torch.bfloat16 and bias.numel() == N and bias.is_contiguous(),
+               "bias must be a contiguous CUDA bfloat16 tensor with N elements")
+    D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    alpha_t = alpha if isinstance(alpha, torch.Tensor) else None
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().sharq_linear_gemm(
+            _ptr(A_comp), _ptr(E), _ptr(SFA_sparse), _ptr(Q_res), _ptr(SF_res), _ptr(QW), _ptr(SFW_sparse),
+            _ptr(SFW_dense), M, N, K, float(alpha_host) if alpha_t is not None else float(alpha) * float(alpha_host),
+            None if alpha_t is None else _scale_ptr(alpha_t, Q_res, "alpha"), _ptr(bias), _ptr(D),
+            _ptr(_error_flag(dev)), _stream(dev)))
+    return D
+
+
+def sharq_linear_forward(x: torch.Tensor, qw: torch.Tensor, sfw_sparse: torch.Tensor, sfw_dense: torch.Tensor,
+                         weight_scale: float) -> torch.Tensor:
+    """Whole SharQ linear on an unscaled bf16 activation [M,K] -> bf16 [M,N]: the optional
+    op the reference's vLLM plugin calls when present (benchmarks/vllm/sharq.py:199-213).
+    Two prepare launches and one GEMM launch; the activation scale stays on the device."""
+    _check(x.dim() == 2, "x must be shaped [M, K]")
+    x = x.contiguous().to(torch.bfloat16)
+    N = int(qw.shape[0])
+    a_comp, e, sfa, q_res, sf_res, scale = scaled_sparse_residual_quantize_x(x, N)
+    return sharq_linear_gemm(a_comp, e, sfa, q_res, sf_res, qw, sfw_sparse, sfw_dense, scale.reshape(1),
+                             alpha_host=float(weight_scale))
+
+
+def set_gemm_tile_n(tile_n: int) -> None:
+    """Force the GEMM tile width (0 = automatic, 128 or 256); test/tuning hook."""
+    _lib.check(_lib.lib().sharq_set_gemm_tile_n(int(tile_n)))
