@@ -1,0 +1,399 @@
+"""Benchmark of the SharQ quantized-linear hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this project's CUDA path
+    python bench.py --impl reference --gpus N --steps K ...  # SHARQ_SIM CPU path (rank 0 only)
+
+Workload (config.workload): the linear layers of a Llama-3-8B-shaped decoder at M tokens
+(default 2048 = batch 1 x seqlen 2048): per layer qkv 6144x4096 and gate_up 28672x4096
+(RMSNorm-fused prepare + fused sparse/residual GEMM), o_proj 4096x4096 and down
+4096x14336 (scaled prepare + GEMM), with config-0 value distributions (X ~ N(0,1) with 1%
+of channels x20, gamma ~ 1+N(0,0.1), W ~ N(0,0.02)).  One step runs all `--layers`
+(default 32) layers, each with its own weights, so the inputs of a step (3.5 GB of packed
+weights) are far larger than L2.  With N > 1 GPUs the layers are tensor-parallel
+(qkv/gate_up column-parallel, o/down row-parallel + NCCL all-reduce); the total work is
+fixed (strong scaling).
+
+metric: dense-equivalent linear throughput, sum(2*M*N*K) / time, in TFLOP/s.
+One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+HIDDEN, FFN, QKV = 4096, 14336, 6144
+SHAPES = {"qkv": (QKV, HIDDEN), "o_proj": (HIDDEN, HIDDEN), "gate_up": (2 * FFN, HIDDEN), "down": (HIDDEN, FFN)}
+METRIC = "sharq_linear_tflops"
+UNIT = "TFLOP/s"
+
+
+def flops_per_layer(m: int) -> float:
+    return sum(2.0 * m * n * k for n, k in SHAPES.values())
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, smax, reasons = [], None, set()
+        for ln in self.lines:
+            f = [c.strip() for c in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------
+# this project's arm
+# ------------------------------------------------------------------------------------------------
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from sharq_b200 import ops
+    from sharq_b200.tp import ColumnParallelSharqLinear, RowParallelSharqLinear, shard_bounds
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the SharQ kernels have no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    m, layers_n = args.tokens, args.layers
+    eps = 1e-6
+
+    # ---- build the layers (same seed on every rank: each rank slices the same full weight)
+    gen = torch.Generator(device=dev).manual_seed(1234)
+    layers = []
+    for _ in range(layers_n):
+        lw = {}
+        for name, (n, k) in SHAPES.items():
+            w = (0.02 * torch.randn(n, k, generator=gen, device=dev)).to(torch.bfloat16)
+            if name in ("qkv", "gate_up"):
+                lw[name] = ColumnParallelSharqLinear(w)
+            else:
+                lw[name] = RowParallelSharqLinear(w)
+            del w
+        lw["gamma1"] = (1 + 0.1 * torch.randn(HIDDEN, generator=gen, device=dev)).to(torch.bfloat16)
+        lw["gamma2"] = (1 + 0.1 * torch.randn(HIDDEN, generator=gen, device=dev)).to(torch.bfloat16)
+        layers.append(lw)
+    torch.cuda.empty_cache()
+
+    # ---- activations (config-0 distribution), host copies pinned for the e2e leg
+    cg = torch.Generator().manual_seed(0)
+
+    def act(rows, cols):
+        x = torch.randn(rows, cols, generator=cg)
+        x[:, torch.randperm(cols, generator=cg)[: cols // 100]] *= 20.0
+        return x.to(torch.bfloat16)
+
+    ob, oe = shard_bounds(HIDDEN, world, rank, 128)
+    db, de = shard_bounds(FFN, world, rank, 128)
+    host = {"h": act(m, HIDDEN).pin_memory(), "o_in": act(m, HIDDEN)[:, ob:oe].contiguous().pin_memory(),
+            "d_in": act(m, FFN)[:, db:de].contiguous().pin_memory()}
+    devx = {k2: v.to(dev) for k2, v in host.items()}
+    out_host = torch.empty((m, HIDDEN), dtype=torch.bfloat16).pin_memory()
+    h2d_bytes = sum(v.numel() * 2 for v in host.values())
+    d2h_bytes = out_host.numel() * 2
+
+    def step(x, timers=None):
+        y = None
+        for lw in layers:
+            for name, inp, gamma in (("qkv", "h", "gamma1"), ("o_proj", "o_in", None), ("gate_up", "h", "gamma2"),
+                                     ("down", "d_in", None)):
+                lin = lw[name]
+                if timers is not None:
+                    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+                    ev[0].record()
+                if gamma is not None:
+                    prep = lin.prepare_input_rmsnorm(x[inp], lw[gamma], eps)
+                else:
+                    prep = lin.local.prepare_input(x[inp])
+                if timers is not None:
+                    ev[1].record()
+                y = lin.local.apply_prepared(prep)
+                if timers is not None:
+                    ev[2].record()
+                    timers.append((name, ev))
+                if gamma is None:
+                    y = lin.reduce(y)
+        return y
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        barrier()
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(max(args.warmup, 3)):
+        step(devx)
+    ops.check_device_errors()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms_total = timed(lambda: step(devx), args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_step = ms_total / args.steps
+    total_flops = flops_per_layer(m) * layers_n
+    value = total_flops / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end: pinned host -> device, step, device -> pinned host, every step
+    def e2e_step():
+        x = {k2: v.to(dev, non_blocking=True) for k2, v in host.items()}
+        y = step(x)
+        out_host.copy_(y, non_blocking=True)
+
+    e2e_step()
+    ms_e2e = timed(e2e_step, args.steps) / args.steps
+    e2e_value = total_flops / (ms_e2e * 1e-3) / 1e12
+
+    # ---- roofline pass: one more step with events around every prepare and GEMM call
+    timers = []
+    step(devx, timers)
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+    peaks = load_peaks()
+    per = {}
+    for name, ev in timers:
+        d = per.setdefault(name, [0.0, 0.0, 0])
+        d[0] += ev[0].elapsed_time(ev[1])
+        d[1] += ev[1].elapsed_time(ev[2])
+        d[2] += 1
+    # dominant kernel: the fused GEMM of gate_up (largest share of the step)
+    n_g, k_g = SHAPES["gate_up"]
+    n_local = n_g // world
+    gemm_ms = per["gate_up"][1] / per["gate_up"][2]
+    # algorithmic work in dense-FP4-equivalent flops: the dense residual pass costs 2MNK, the
+    # sparse main pass 2MNK at twice the rate => 3*M*N*K per launch
+    alg_flops = 3.0 * m * n_local * k_g
+    p_dense_fp4 = 4.0 * peaks["bf16_tflops_sustained"]  # dense FP4 : bf16 tensor rate is 4 : 1 on this part
+    achieved = alg_flops / (gemm_ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": "gemm_kernel<256,sparse+dense> (gate_up)", "achieved": round(achieved, 1),
+                "peak": round(p_dense_fp4, 1), "unit": "TFLOP/s", "frac": round(achieved / p_dense_fp4, 4),
+                "traffic": None,
+                "peak_source": f"4 x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS (dense FP4 = 4 x bf16 rate)",
+                "flops_convention": "3*M*N*K dense-FP4-equivalent (2MNK dense pass + 2MNK sparse pass at 2x rate)",
+                "avg_launch_ms": round(gemm_ms, 4)}
+    prep_ms = per["gate_up"][0] / per["gate_up"][2]
+    prep_bytes = 2.906 * m * HIDDEN
+    gemm_share = sum(v[1] for v in per.values()) / max(1e-9, sum(v[0] + v[1] for v in per.values()))
+    extra = {
+        "prepare_rmsnorm": {"bound": "hbm", "achieved": round(prep_bytes / (prep_ms * 1e-3) / 1e9, 1),
+                            "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                            "frac": round(prep_bytes / (prep_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                            "avg_ms_two_launches": round(prep_ms, 4)},
+        "per_linear_ms": {k2: {"prepare": round(v[0] / v[2], 4), "gemm": round(v[1] / v[2], 4)} for k2, v in per.items()},
+        "gemm_time_share": round(gemm_share, 3),
+    }
+
+    result = {
+        "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4", "data": "synthetic",
+        "config": {"workload": f"llama3-8b linear layers (qkv 6144x4096, o 4096x4096, gate_up 28672x4096, "
+                               f"down 4096x14336), M={m} tokens, {layers_n} layers per step, SharQ W4A4, RMSNorm fused",
+                   "parallelism": f"tp{world}", "l2": "inputs larger than L2: every layer has its own weights "
+                                                      f"({layers_n} x 109 MB packed), no flush needed",
+                   "tokens_per_s_linear_path": round(m / (ms_step * 1e-3), 1)},
+        "roofline": roofline, "roofline_extra": extra,
+        "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": h2d_bytes,
+                "d2h_bytes_per_step": d2h_bytes, "ms_per_step": round(ms_e2e, 4)},
+        "gpu_launches": args.steps * layers_n * 12,
+        "clocks": clocks,
+    }
+    if rank == 0:
+        if world == 1:
+            result["cpu_baseline"] = cpu_baseline(seconds=args.cpu_seconds)
+        print(json.dumps(result), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline / reference arm: the SHARQ_SIM fake-quant path (oracle port) on the host cores
+# ------------------------------------------------------------------------------------------------
+
+def cpu_baseline(seconds: float = 12.0, m: int = 128):
+    """SHARQ_SIM linear (RMSNorm + activation split + two bf16 matmuls) on the host cores."""
+    import torch
+
+    from oracle import sharq_sim as S
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(0)
+    n, k = HIDDEN, HIDDEN
+    x = torch.randn(m, k, generator=g)
+    x[:, torch.randperm(k, generator=g)[: k // 100]] *= 20.0
+    x = x.to(torch.bfloat16)
+    gamma = (1 + 0.1 * torch.randn(k, generator=g)).to(torch.bfloat16)
+    w = (0.02 * torch.randn(n, k, generator=g)).to(torch.bfloat16)
+    w_q, s_w = S.quantize_weight(w)  # offline, untimed
+
+    def one():
+        xn = S.rmsnorm(x, gamma, 1e-6)
+        main, res, s_x = S.quantize_activation(xn)
+        return S.linear(main, res, s_x, w_q, s_w)
+
+    one()
+    t0 = time.perf_counter()
+    it = 0
+    while time.perf_counter() - t0 < seconds or it < 3:
+        one()
+        it += 1
+    dt = (time.perf_counter() - t0) / it
+    return {"value": round(2.0 * m * n * k / dt / 1e12, 5), "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"SHARQ_SIM layer (oracle/sharq_sim.py), M={m}, K=N=4096, {it} iterations, weights pre-quantised"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+
+    from oracle import sharq_sim as S
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    m = args.ref_tokens
+    g = torch.Generator().manual_seed(0)
+
+    def act(rows, cols):
+        x = torch.randn(rows, cols, generator=g)
+        x[:, torch.randperm(cols, generator=g)[: cols // 100]] *= 20.0
+        return x.to(torch.bfloat16)
+
+    xs = {"h": act(m, HIDDEN), "o_in": act(m, HIDDEN), "d_in": act(m, FFN)}
+    gamma = (1 + 0.1 * torch.randn(HIDDEN, generator=g)).to(torch.bfloat16)
+    weights = {}
+    for name, (n, k) in SHAPES.items():
+        weights[name] = S.quantize_weight((0.02 * torch.randn(n, k, generator=g)).to(torch.bfloat16))
+
+    def step():
+        y = None
+        for name, inp, norm in (("qkv", "h", True), ("o_proj", "o_in", False), ("gate_up", "h", True), ("down", "d_in", False)):
+            x = S.rmsnorm(xs[inp], gamma, 1e-6) if norm else xs[inp]
+            main, res, s_x = S.quantize_activation(x)
+            y = S.linear(main, res, s_x, *weights[name])
+        return y
+
+    for _ in range(max(1, min(args.warmup, 2))):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = flops_per_layer(m) / dt / 1e12
+    sample = (f"one decoder layer's four linears through the SHARQ_SIM port (oracle/sharq_sim.py) at M={m} tokens "
+              f"per step on {cores} host threads; weights pre-quantised")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": round(value, 5), "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": max(1, min(args.warmup, 2)), "ms_per_step": round(dt * 1e3, 3),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 fake-quant (SHARQ_SIM)",
+        "data": "synthetic",
+        "config": {"workload": "llama3-8b linear layers (qkv, o, gate_up, down), SHARQ_SIM on host CPU, "
+                               f"bounded sample M={m} tokens, 1 layer per step"},
+        "cpu_baseline": {"value": round(value, 5), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": round(value, 5), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--ref-tokens", type=int, default=128)
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
