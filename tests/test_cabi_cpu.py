@@ -1,0 +1,56 @@
+"""The C-ABI library builds for sm_100a without a GPU, loads, and exports every symbol that
+include/sharq_b200.h declares; the ctypes table matches the header; argument checks that
+need no device work."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def header_symbols():
+    text = (ROOT / "include" / "sharq_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(sharq_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from sharq_b200 import _build, _lib
+
+    _build.build()
+    lib = ctypes.CDLL(str(_lib.LIB_PATH))
+    names = header_symbols()
+    assert len(names) >= 17
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/sharq_b200.h but not exported"
+    assert sorted(_lib.SIGNATURES) == names, "ctypes signature table out of sync with the header"
+
+
+def test_size_queries_and_argument_errors_without_gpu():
+    from sharq_b200 import _lib, ops
+
+    assert _lib.lib().sharq_version() >= 100
+    assert ops.get_fused_sparse_residual_buffer_sizes(512, 4096, 4096) == (524288, 131072, 163840, 1048576, 163840)
+    assert ops.get_sparse_nvfp4_buffer_sizes(130, 256, 512) == (16640, 8192, 8192, 12288)
+    assert _lib.lib().sharq_prepare_workspace_bytes(100) == 256 + 400
+    L = _lib.lib()
+    # K not a multiple of 128 is rejected before any launch
+    rc = L.sharq_fused_sparse_residual_quantize_x(None, 4, 4, 96, None, None, None, None, None, None)
+    assert rc != 0 and b"multiple of 128" in L.sharq_last_error()
+    rc = L.sharq_sparse_matmul(None, None, None, None, None, 128, 128, 256, 1.0, None, 1.0, None, None, None)
+    assert rc != 0 and b"beta == 0" in L.sharq_last_error()
+    with pytest.raises(_lib.SharqError):
+        _lib.check(L.sharq_set_gemm_tile_n(64))
+
+
+def test_ops_reject_cpu_tensors():
+    import torch
+
+    from sharq_b200 import ops
+
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        ops.fused_sparse_residual_quantize_x(torch.zeros(4, 128, dtype=torch.bfloat16), 64)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        ops.quantize_w32_shared(torch.zeros(4, 128, dtype=torch.bfloat16))
