@@ -118,6 +118,23 @@ int sharq_linear_gemm(const void *a_comp, const void *e, const void *sfa_sparse,
                       int k, float alpha, const float *alpha_dev, const void *bias_bf16, void *d, int *error_flag,
                       void *stream);
 
+/* No counterpart in the reference.  Same work and outputs as
+ * sharq_fused_rmsnorm_sparse_residual_quantize_x, for callers that cannot allocate device
+ * memory and have no spare buffer to pass as workspace (a server that has given all free
+ * HBM to its own pool; a thread on which cudaMalloc's device-wide synchronisation is not
+ * allowed): the scratch lives in a fixed array inside the library (256 KiB + 256 B per GPU
+ * that loads it).  M <= sharq_noalloc_max_rows() (65536), larger M is an error.  The first
+ * call on a device looks up the array's address and should come before any stream capture;
+ * no call allocates.  All calls on a device share the array: calls that overlap on the GPU
+ * race, so order them on one stream (or with events).  Errors: non-zero return,
+ * message from sharq_noalloc_last_error(). */
+int sharq_fused_rmsnorm_sparse_residual_quantize_x_noalloc(const void *x_bf16, const void *rmsnorm_weight_bf16,
+                                                           float rmsnorm_eps, int m, int n, int k, void *a_comp,
+                                                           void *e, void *sfa_sparse, void *q_res, void *sf_res,
+                                                           float *scale_out, void *stream);
+int sharq_noalloc_max_rows(void);
+const char *sharq_noalloc_last_error(void);
+
 /* Test/tuning hook: force the GEMM tile width (0 = automatic, 128 or 256).  Process-wide. */
 int sharq_set_gemm_tile_n(int tile_n);
 

@@ -36,6 +36,10 @@ SIGNATURES = {
     "sharq_linear_gemm": (
         c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_float, _P, _P, _P, _P, _P]),
     "sharq_set_gemm_tile_n": (c_int, [c_int]),
+    "sharq_fused_rmsnorm_sparse_residual_quantize_x_noalloc": (
+        c_int, [_P, _P, c_float, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P]),
+    "sharq_noalloc_max_rows": (c_int, []),
+    "sharq_noalloc_last_error": (c_char_p, []),
 }
 
 
