@@ -66,7 +66,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:
@@ -203,15 +203,16 @@ def run_ours(args):
             ms = float(t.item())
         return ms
 
+    # clocks are sampled from before the warm-up until after the end-to-end leg, so that the
+    # samples cover the timed regions even when those last only a fraction of a second
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(max(args.warmup, 3)):
         step(devx)
     ops.check_device_errors()
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     ms_total = timed(lambda: step(devx), args.steps)
-    clocks = sampler.stop() if rank == 0 else None
     ms_step = ms_total / args.steps
     total_flops = flops_per_layer(m) * layers_n
     value = total_flops / (ms_step * 1e-3) / 1e12
@@ -225,6 +226,7 @@ def run_ours(args):
     e2e_step()
     ms_e2e = timed(e2e_step, args.steps) / args.steps
     e2e_value = total_flops / (ms_e2e * 1e-3) / 1e12
+    clocks = sampler.stop() if rank == 0 else None
 
     # ---- roofline pass: one more step with events around every prepare and GEMM call
     timers = []

@@ -135,7 +135,8 @@ int sharq_fused_rmsnorm_sparse_residual_quantize_x_noalloc(const void *x_bf16, c
 int sharq_noalloc_max_rows(void);
 const char *sharq_noalloc_last_error(void);
 
-/* Test/tuning hook: force the GEMM tile width (0 = automatic, 128 or 256).  Process-wide. */
+/* Test/tuning hook: force the GEMM kernel variant (0 = automatic; 128 or 256 = single-CTA kernel
+ * with that tile width; 512 = CTA-pair kernel, 256 x 256 tile per pair).  Process-wide. */
 int sharq_set_gemm_tile_n(int tile_n);
 
 #ifdef __cplusplus

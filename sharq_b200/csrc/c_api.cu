@@ -152,7 +152,7 @@ int sharq_compress_sparse_a(const void *a_q_dense, int m, int n, int k, void *a_
 }
 
 int sharq_set_gemm_tile_n(int tile_n) {
-  SHARQ_REQUIRE(tile_n == 0 || tile_n == 128 || tile_n == 256, "tile_n must be 0, 128 or 256");
+  SHARQ_REQUIRE(tile_n == 0 || tile_n == 128 || tile_n == 256 || tile_n == 512, "tile_n must be 0, 128, 256 or 512");
   g_tile_n = tile_n;
   return 0;
 }

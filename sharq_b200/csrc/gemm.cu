@@ -7,16 +7,27 @@
 //   kernels/src/nvfp4.cu:432-455, kernels/src/sparse_nvfp4.cu:436-460 and the two-launch
 //   composition at model/qLinearLayer.py:130-154.
 //
-// Kernel shape (one output tile of 128 x BN per CTA, K consumed in stages of 256):
-//   warp 0    TMA producer: per stage three tensor-map loads (weight tile, dense A tile,
-//             compressed A tile; 128-byte / 64-byte swizzle) and plain bulk copies of the
-//             metadata tile and the scale-factor tiles, all landing on one mbarrier.
-//   warp 1    MMA issuer: copies metadata and scale factors shared -> tensor memory
-//             (tcgen05.cp), then issues 2 sparse (K=128) and 4 dense (K=64) MMAs per stage
-//             into the same accumulator; tcgen05.commit releases the stage.
-//   warps 2-5 epilogue: tcgen05.ld the accumulator, alpha/beta/bias, bf16, store.
-// All mbarrier waits are bounded; a timed-out wait sets *error_flag and every role
-// drains to the common exit, where tensor memory is released.
+// One persistent kernel, one CTA per SM (or one CTA pair per SM pair), looping over output
+// tiles with the M index fastest so that CTAs working at the same time share weight tiles
+// in L2.  K is consumed in stages of 256.  Warp roles:
+//   warp 0     TMA producer: per stage three tensor-map loads (weight tile, dense A tile,
+//              compressed A tile; 128-byte / 64-byte swizzle) and plain bulk copies of the
+//              metadata tile and the scale-factor tiles, all landing on one mbarrier.  It runs
+//              ahead across tile boundaries, so the pipeline never drains between tiles.
+//   warp 1     MMA issuer: copies metadata and scale factors shared -> tensor memory
+//              (tcgen05.cp), then issues 2 sparse (K=128) and 4 dense (K=64) MMAs per stage
+//              into the same accumulator; tcgen05.commit releases the stage.
+//   warps 2-9  epilogue: pull the whole accumulator into registers with tcgen05.ld, hand the
+//              tensor memory back to the MMA warp at once, then alpha/beta/bias, bf16 and the
+//              global stores overlap the next tile's MMAs.
+// CTA-pair mode (cta_group::2, cluster of 2): the pair computes a 256 x 256 tile; CTA r owns
+// rows [128r,128r+128) (its A operands, scales, metadata, accumulator) and loads weight rows
+// [128r,128r+128) of the tile; the tensor cores of both SMs read both halves.  Every CTA
+// loads with its own plain TMA copies - there is no multicast load anywhere.  Hand-shake:
+// the peer CTA reports each loaded stage on the leader's peer barrier, the leader issues
+// the pair's MMAs and commits to the barriers of both CTAs.
+// All mbarrier waits are bounded; a timed-out wait sets *error_flag and every role drains
+// to the common exit, where tensor memory is released.
 #include "common.cuh"
 #include "gemm.cuh"
 #include "sm100_ptx.cuh"
@@ -29,13 +40,17 @@ namespace sharq {
 namespace {
 
 constexpr int kBM = 128;
-constexpr int kBK = 256;           // logical K per stage
-constexpr int kGemmThreads = 192;  // 6 warps
+constexpr int kBK = 256;  // logical K per stage
+constexpr int kEpiWarps = 8;
+constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 
-template <int BN, bool SPARSE, bool DENSE>
+// Shared-memory stage and tensor-memory column layout.  In pair mode BN is the pair's tile
+// width (256) and each CTA stores half of the weight tile.
+template <int BN, bool SPARSE, bool DENSE, bool PAIR>
 struct StageLayout {
-  static constexpr int kBands = BN / 128;
-  static constexpr int kWBytes = BN * 128;
+  static constexpr int kBands = BN / 128;  // 128-row scale-factor bands of the weight tile
+  static constexpr int kWRows = PAIR ? BN / 2 : BN;
+  static constexpr int kWBytes = kWRows * 128;
   static constexpr int kADenseBytes = DENSE ? kBM * 128 : 0;
   static constexpr int kACompBytes = SPARSE ? kBM * 64 : 0;
   static constexpr int kEBytes = SPARSE ? 2048 : 0;
@@ -52,7 +67,9 @@ struct StageLayout {
   static constexpr int kOffSfaD = kOffSfbSp + kSfbSpBytes;
   static constexpr int kOffSfbD = kOffSfaD + kSfaDBytes;
   static constexpr int kStageBytes = (kOffSfbD + kSfbDBytes + 1023) / 1024 * 1024;
-  static constexpr int kStages = (BN == 256) ? (SPARSE && DENSE ? 3 : 4) : 4;
+  static constexpr int kMaxSmem = 227 * 1024 - 2048;
+  static constexpr int kStagesFit = kMaxSmem / kStageBytes;
+  static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
   // tensor memory columns
   static constexpr int kColAcc = 0;
   static constexpr int kColE = BN;
@@ -62,7 +79,7 @@ struct StageLayout {
   static constexpr int kColSfbD = kColSfaD + 16;
   static constexpr int kColEnd = kColSfbD + 4 * (BN / 32);
   static constexpr int kTmemCols = kColEnd <= 256 ? 256 : 512;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
 };
 
 struct GemmParams {
@@ -81,45 +98,111 @@ struct GemmParams {
   int *error_flag;
 };
 
-template <int BN, bool SPARSE, bool DENSE>
+// Epilogue of 32 accumulator columns held in registers: d = bf16(alpha * acc + beta * c_in),
+// then (+ bias) in bf16; rows >= M and columns >= N are masked.  A thread owns one row and
+// stores 64 contiguous bytes.
+__device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32_t *acc, int row, int col0, float alpha,
+                                               float beta, bool has_c) {
+  if (row >= p.m || col0 >= p.n) return;
+  const size_t off = (size_t)row * p.n + col0;
+  const bool full = (col0 + 32 <= p.n) && ((p.n & 7) == 0);
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {  // 8 columns per 16-byte store
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = alpha * __uint_as_float(acc[8 * v + i]);
+    if (has_c) {
+      if (full) {
+        uint4 cv = *reinterpret_cast<const uint4 *>(p.c_in + off + 8 * v);
+        uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          f[2 * i] = __fmaf_rn(beta, bf16_bits_to_float(cw[i] & 0xFFFFu), f[2 * i]);
+          f[2 * i + 1] = __fmaf_rn(beta, bf16_bits_to_float(cw[i] >> 16), f[2 * i + 1]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (col0 + 8 * v + i < p.n) f[i] = __fmaf_rn(beta, __bfloat162float(p.c_in[off + 8 * v + i]), f[i]);
+      }
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t lo = float_to_bf16_bits(f[2 * i]), hi = float_to_bf16_bits(f[2 * i + 1]);
+      if (p.bias != nullptr) {
+        // bias is added to the bf16 result, as a separate bf16 add would
+        const int cc = col0 + 8 * v + 2 * i;
+        float b0 = cc < p.n ? __bfloat162float(p.bias[cc]) : 0.0f;
+        float b1 = cc + 1 < p.n ? __bfloat162float(p.bias[cc + 1]) : 0.0f;
+        lo = float_to_bf16_bits(bf16_bits_to_float(lo) + b0);
+        hi = float_to_bf16_bits(bf16_bits_to_float(hi) + b1);
+      }
+      o[i] = lo | (hi << 16);
+    }
+    if (full) {
+      *reinterpret_cast<uint4 *>(p.d + off + 8 * v) = make_uint4(o[0], o[1], o[2], o[3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (col0 + 8 * v + i < p.n)
+          p.d[off + 8 * v + i] = __ushort_as_bfloat16((unsigned short)((o[i >> 1] >> (16 * (i & 1))) & 0xFFFFu));
+    }
+  }
+}
+
+template <int BN, bool SPARSE, bool DENSE, bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a_dense,
                 const __grid_constant__ CUtensorMap tm_a_comp, const GemmParams p) {
-  using L = StageLayout<BN, SPARSE, DENSE>;
+  using L = StageLayout<BN, SPARSE, DENSE, PAIR>;
   constexpr int S = L::kStages;
+  constexpr int CG = PAIR ? 2 : 1;
+  constexpr int kColsPerEpiWarp = BN / 2;  // two warps share each tensor-memory lane quadrant
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + S * L::kStageBytes);
   uint64_t *empty_bar = full_bar + S;
-  uint64_t *acc_bar = empty_bar + S;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_bar + 1);
+  uint64_t *peer_bar = empty_bar + S;  // pair mode, leader CTA: "the peer has loaded stage s"
+  uint64_t *acc_full_bar = peer_bar + S;
+  uint64_t *acc_empty_bar = acc_full_bar + 1;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty_bar + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n_tile = blockIdx.x;
-  const int m_tile = blockIdx.y;
+  const uint32_t cta_rank = PAIR ? ptx::cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0;
   const int k_stages = (p.k + kBK - 1) / kBK;
   const int aligned_m = (p.m + 127) / 128 * 128;
   const int tiles_sp = p.k / 128;  // 512-byte scale tiles per 128-row band, 32-group layout
   const int tiles_d = p.k / 64;    // same, 16-group layout
+  // work units: a unit is one output tile of a CTA (128 x BN) or of a pair (256 x BN)
+  const int m_units = PAIR ? (p.m + 255) / 256 : (p.m + kBM - 1) / kBM;
+  const int n_tiles = (p.n + BN - 1) / BN;
+  const int num_units = m_units * n_tiles;
+  const int unit0 = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int unit_stride = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       ptx::mbar_init(full_bar + s, 1);
       ptx::mbar_init(empty_bar + s, 1);
+      ptx::mbar_init(peer_bar + s, 1);
     }
-    ptx::mbar_init(acc_bar, 1);
+    ptx::mbar_init(acc_full_bar, 1);
+    ptx::mbar_init(acc_empty_bar, PAIR ? 2 * kEpiWarps : kEpiWarps);
     *abort_flag = 0;
     ptx::fence_barrier_init();
   }
   if (warp == 1) {
-    ptx::tmem_alloc<1>(tmem_slot, L::kTmemCols);
-    ptx::tmem_relinquish<1>();
+    ptx::tmem_alloc<CG>(tmem_slot, L::kTmemCols);
+    ptx::tmem_relinquish<CG>();
   }
   ptx::tc_fence_before();
   __syncthreads();
+  if (PAIR) ptx::cluster_sync();  // both CTAs' barriers exist before any remote arrive
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -129,183 +212,223 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       ptx::tma_prefetch_desc(&tm_w);
       if (DENSE) ptx::tma_prefetch_desc(&tm_a_dense);
       if (SPARSE) ptx::tma_prefetch_desc(&tm_a_comp);
-      for (int it = 0; it < k_stages; ++it) {
-        const int s = it % S;
-        const uint32_t ph = (uint32_t)(it / S) & 1u;
-        if (!ptx::mbar_wait(empty_bar + s, ph ^ 1u, abort_flag)) {
-          *abort_flag = 1;
-          atomicExch(p.error_flag, 1);
-          break;
-        }
-        uint8_t *st = smem + s * L::kStageBytes;
-        const int n_sp = SPARSE ? min(2, tiles_sp - 2 * it) : 0;
-        const int n_d = DENSE ? min(4, tiles_d - 4 * it) : 0;
-        uint32_t tx = L::kWBytes + L::kADenseBytes + L::kACompBytes + L::kEBytes;
-        tx += (uint32_t)(n_sp * 512 * (1 + L::kBands) + n_d * 512 * (1 + L::kBands));
-        ptx::mbar_arrive_expect_tx(full_bar + s, tx);
-        ptx::tma_load_2d(st + L::kOffW, &tm_w, it * 128, n_tile * BN, full_bar + s);
-        if (DENSE) {
-          ptx::tma_load_2d(st + L::kOffADense, &tm_a_dense, it * 128, m_tile * kBM, full_bar + s);
-          ptx::bulk_load_1d(st + L::kOffSfaD, p.sfa_dense + ((size_t)m_tile * tiles_d + 4 * (size_t)it) * 512,
-                            (uint32_t)n_d * 512, full_bar + s);
-          for (int b = 0; b < L::kBands; ++b)
-            ptx::bulk_load_1d(st + L::kOffSfbD + b * 2048,
-                              p.sfb_dense + ((size_t)(n_tile * L::kBands + b) * tiles_d + 4 * (size_t)it) * 512,
+      uint32_t g = 0;  // stages issued so far, across tiles
+      bool ok = true;
+      for (int u = unit0; u < num_units && ok; u += unit_stride) {
+        const int m_tile = PAIR ? 2 * (u % m_units) + (int)cta_rank : (u % m_units);
+        const int n_tile = u / m_units;
+        const int w_row = n_tile * BN + (PAIR ? (int)cta_rank * (BN / 2) : 0);
+        for (int it = 0; it < k_stages; ++it, ++g) {
+          const int s = (int)(g % S);
+          const uint32_t ph = (g / S) & 1u;
+          if (!ptx::mbar_wait(empty_bar + s, ph ^ 1u, abort_flag)) {
+            *abort_flag = 1;
+            atomicExch(p.error_flag, 1);
+            ok = false;
+            break;
+          }
+          uint8_t *st = smem + s * L::kStageBytes;
+          const int n_sp = SPARSE ? min(2, tiles_sp - 2 * it) : 0;
+          const int n_d = DENSE ? min(4, tiles_d - 4 * it) : 0;
+          uint32_t tx = L::kWBytes + L::kADenseBytes + L::kACompBytes + L::kEBytes;
+          tx += (uint32_t)(n_sp * 512 * (1 + L::kBands) + n_d * 512 * (1 + L::kBands));
+          ptx::mbar_arrive_expect_tx(full_bar + s, tx);
+          ptx::tma_load_2d(st + L::kOffW, &tm_w, it * 128, w_row, full_bar + s);
+          if (DENSE) {
+            ptx::tma_load_2d(st + L::kOffADense, &tm_a_dense, it * 128, m_tile * kBM, full_bar + s);
+            ptx::bulk_load_1d(st + L::kOffSfaD, p.sfa_dense + ((size_t)m_tile * tiles_d + 4 * (size_t)it) * 512,
                               (uint32_t)n_d * 512, full_bar + s);
-        }
-        if (SPARSE) {
-          ptx::tma_load_2d(st + L::kOffAComp, &tm_a_comp, it * 64, m_tile * kBM, full_bar + s);
-          ptx::bulk_load_1d(st + L::kOffE, p.e + ((size_t)it * aligned_m + (size_t)m_tile * 128) * 16, 2048,
-                            full_bar + s);
-          ptx::bulk_load_1d(st + L::kOffSfaSp, p.sfa_sparse + ((size_t)m_tile * tiles_sp + 2 * (size_t)it) * 512,
-                            (uint32_t)n_sp * 512, full_bar + s);
-          for (int b = 0; b < L::kBands; ++b)
-            ptx::bulk_load_1d(st + L::kOffSfbSp + b * 1024,
-                              p.sfb_sparse + ((size_t)(n_tile * L::kBands + b) * tiles_sp + 2 * (size_t)it) * 512,
+#pragma unroll
+            for (int b = 0; b < L::kBands; ++b)
+              ptx::bulk_load_1d(st + L::kOffSfbD + b * 2048,
+                                p.sfb_dense + ((size_t)(n_tile * L::kBands + b) * tiles_d + 4 * (size_t)it) * 512,
+                                (uint32_t)n_d * 512, full_bar + s);
+          }
+          if (SPARSE) {
+            ptx::tma_load_2d(st + L::kOffAComp, &tm_a_comp, it * 64, m_tile * kBM, full_bar + s);
+            ptx::bulk_load_1d(st + L::kOffE, p.e + ((size_t)it * aligned_m + (size_t)m_tile * 128) * 16, 2048,
+                              full_bar + s);
+            ptx::bulk_load_1d(st + L::kOffSfaSp, p.sfa_sparse + ((size_t)m_tile * tiles_sp + 2 * (size_t)it) * 512,
                               (uint32_t)n_sp * 512, full_bar + s);
+#pragma unroll
+            for (int b = 0; b < L::kBands; ++b)
+              ptx::bulk_load_1d(st + L::kOffSfbSp + b * 1024,
+                                p.sfb_sparse + ((size_t)(n_tile * L::kBands + b) * tiles_sp + 2 * (size_t)it) * 512,
+                                (uint32_t)n_sp * 512, full_bar + s);
+          }
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
     if (ptx::elect_one()) {
-      constexpr uint32_t idesc_d = ptx::make_idesc_nvf4(kBM, BN, false);
-      constexpr uint32_t idesc_s = ptx::make_idesc_nvf4(kBM, BN, true);
-      uint32_t accumulate = 0;
-      bool ok = true;
-      for (int it = 0; it < k_stages && ok; ++it) {
-        const int s = it % S;
-        const uint32_t ph = (uint32_t)(it / S) & 1u;
-        if (!ptx::mbar_wait(full_bar + s, ph, abort_flag)) {
-          *abort_flag = 1;
-          atomicExch(p.error_flag, 2);
-          ok = false;
-          break;
-        }
-        ptx::tc_fence_after();
-        const uint32_t st = ptx::smem_u32(smem + s * L::kStageBytes);
-        const int n_sp = SPARSE ? min(2, tiles_sp - 2 * it) : 0;
-        const int n_d = DENSE ? min(4, tiles_d - 4 * it) : 0;
-        if (SPARSE) {
-          ptx::tmem_cp_128x128b<1>(tmem_base + L::kColE, ptx::make_smem_desc(st + L::kOffE, 128, 0, 0));
-          for (int t = 0; t < n_sp; ++t) {
-            ptx::tmem_cp_32x128b_warpx4<1>(tmem_base + L::kColSfaSp + 4 * t,
-                                           ptx::make_smem_desc(st + L::kOffSfaSp + t * 512, 128, 0, 0));
-            for (int b = 0; b < L::kBands; ++b)
-              ptx::tmem_cp_32x128b_warpx4<1>(tmem_base + L::kColSfbSp + t * (BN / 32) + 4 * b,
-                                             ptx::make_smem_desc(st + L::kOffSfbSp + b * 1024 + t * 512, 128, 0, 0));
+      if (PAIR && !leader) {
+        // ---------------------------------------------------------- peer CTA: report loaded stages
+        uint32_t g = 0;
+        bool ok = true;
+        for (int u = unit0; u < num_units && ok; u += unit_stride) {
+          for (int it = 0; it < k_stages; ++it, ++g) {
+            const int s = (int)(g % S);
+            if (!ptx::mbar_wait(full_bar + s, (g / S) & 1u, abort_flag)) {
+              *abort_flag = 1;
+              atomicExch(p.error_flag, 4);
+              ok = false;
+              break;
+            }
+            ptx::mbar_arrive_cluster(peer_bar + s, 0);
           }
         }
-        if (DENSE) {
-          for (int t = 0; t < n_d; ++t) {
-            ptx::tmem_cp_32x128b_warpx4<1>(tmem_base + L::kColSfaD + 4 * t,
-                                           ptx::make_smem_desc(st + L::kOffSfaD + t * 512, 128, 0, 0));
-            for (int b = 0; b < L::kBands; ++b)
-              ptx::tmem_cp_32x128b_warpx4<1>(tmem_base + L::kColSfbD + t * (BN / 32) + 4 * b,
-                                             ptx::make_smem_desc(st + L::kOffSfbD + b * 2048 + t * 512, 128, 0, 0));
+      } else {
+        // ---------------------------------------------------------- MMA issuer
+        constexpr uint32_t idesc_d = ptx::make_idesc_nvf4(PAIR ? 256 : kBM, BN, false);
+        constexpr uint32_t idesc_s = ptx::make_idesc_nvf4(PAIR ? 256 : kBM, BN, true);
+        uint32_t g = 0;
+        uint32_t tile_iter = 0;
+        bool ok = true;
+        for (int u = unit0; u < num_units && ok; u += unit_stride, ++tile_iter) {
+          // the epilogue warps must have pulled the previous tile out of tensor memory
+          const bool drained = PAIR ? ptx::mbar_wait_cluster(acc_empty_bar, (tile_iter & 1u) ^ 1u, abort_flag)
+                                    : ptx::mbar_wait(acc_empty_bar, (tile_iter & 1u) ^ 1u, abort_flag);
+          if (!drained) {
+            *abort_flag = 1;
+            atomicExch(p.error_flag, 5);
+            break;
+          }
+          ptx::tc_fence_after();
+          uint32_t accumulate = 0;
+          for (int it = 0; it < k_stages; ++it, ++g) {
+            const int s = (int)(g % S);
+            const uint32_t ph = (g / S) & 1u;
+            bool got = ptx::mbar_wait(full_bar + s, ph, abort_flag);
+            if (PAIR && got) got = ptx::mbar_wait_cluster(peer_bar + s, ph, abort_flag);
+            if (!got) {
+              *abort_flag = 1;
+              atomicExch(p.error_flag, 2);
+              ok = false;
+              break;
+            }
+            ptx::tc_fence_after();
+            const uint32_t st = ptx::smem_u32(smem + s * L::kStageBytes);
+            const int n_sp = SPARSE ? min(2, tiles_sp - 2 * it) : 0;
+            const int n_d = DENSE ? min(4, tiles_d - 4 * it) : 0;
+            if (SPARSE) {
+              ptx::tmem_cp_128x128b<CG>(tmem_base + L::kColE, ptx::make_smem_desc(st + L::kOffE, 128, 0, 0));
+#pragma unroll
+              for (int t = 0; t < 2; ++t) {
+                if (t < n_sp) {
+                  ptx::tmem_cp_32x128b_warpx4<CG>(tmem_base + L::kColSfaSp + 4 * t,
+                                                  ptx::make_smem_desc(st + L::kOffSfaSp + t * 512, 128, 0, 0));
+#pragma unroll
+                  for (int b = 0; b < L::kBands; ++b)
+                    ptx::tmem_cp_32x128b_warpx4<CG>(
+                        tmem_base + L::kColSfbSp + t * (BN / 32) + 4 * b,
+                        ptx::make_smem_desc(st + L::kOffSfbSp + b * 1024 + t * 512, 128, 0, 0));
+                }
+              }
+            }
+            if (DENSE) {
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                if (t < n_d) {
+                  ptx::tmem_cp_32x128b_warpx4<CG>(tmem_base + L::kColSfaD + 4 * t,
+                                                  ptx::make_smem_desc(st + L::kOffSfaD + t * 512, 128, 0, 0));
+#pragma unroll
+                  for (int b = 0; b < L::kBands; ++b)
+                    ptx::tmem_cp_32x128b_warpx4<CG>(
+                        tmem_base + L::kColSfbD + t * (BN / 32) + 4 * b,
+                        ptx::make_smem_desc(st + L::kOffSfbD + b * 2048 + t * 512, 128, 0, 0));
+                }
+              }
+            }
+            if (SPARSE) {
+              // compressed A: 64-byte swizzled rows, 32 bytes (128 logical K) per MMA;
+              // weight: 128-byte swizzled rows, 64 bytes (128 K) per MMA.
+#pragma unroll
+              for (int t = 0; t < 2; ++t) {
+                if (t < n_sp) {
+                  uint64_t da = ptx::make_smem_desc(st + L::kOffAComp + t * 32, 512, 16, 4);
+                  uint64_t db = ptx::make_smem_desc(st + L::kOffW + t * 64, 1024, 16, 2);
+                  ptx::mma_nvf4_sparse<CG>(tmem_base + L::kColAcc, da, db, idesc_s, tmem_base + L::kColSfaSp + 4 * t,
+                                           tmem_base + L::kColSfbSp + t * (BN / 32), tmem_base + L::kColE + 2 * t,
+                                           accumulate);
+                  accumulate = 1;
+                }
+              }
+            }
+            if (DENSE) {
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                if (t < n_d) {
+                  uint64_t da = ptx::make_smem_desc(st + L::kOffADense + t * 32, 1024, 16, 2);
+                  uint64_t db = ptx::make_smem_desc(st + L::kOffW + t * 32, 1024, 16, 2);
+                  ptx::mma_nvf4_dense<CG>(tmem_base + L::kColAcc, da, db, idesc_d, tmem_base + L::kColSfaD + 4 * t,
+                                          tmem_base + L::kColSfbD + t * (BN / 32), accumulate);
+                  accumulate = 1;
+                }
+              }
+            }
+            if (PAIR)
+              ptx::tc_commit_multicast2(empty_bar + s, 3);
+            else
+              ptx::tc_commit<1>(empty_bar + s);
+          }
+          if (ok) {
+            if (PAIR)
+              ptx::tc_commit_multicast2(acc_full_bar, 3);
+            else
+              ptx::tc_commit<1>(acc_full_bar);
           }
         }
-        if (SPARSE) {
-          // compressed A: 64-byte swizzled rows, 32 bytes (128 logical K) per MMA;
-          // weight: 128-byte swizzled rows, 64 bytes (128 K) per MMA.
-          for (int t = 0; t < n_sp; ++t) {
-            uint64_t da = ptx::make_smem_desc(st + L::kOffAComp + t * 32, 512, 16, 4);
-            uint64_t db = ptx::make_smem_desc(st + L::kOffW + t * 64, 1024, 16, 2);
-            ptx::mma_nvf4_sparse<1>(tmem_base + L::kColAcc, da, db, idesc_s, tmem_base + L::kColSfaSp + 4 * t,
-                                    tmem_base + L::kColSfbSp + t * (BN / 32), tmem_base + L::kColE + 2 * t, accumulate);
-            accumulate = 1;
-          }
-        }
-        if (DENSE) {
-          for (int t = 0; t < n_d; ++t) {
-            uint64_t da = ptx::make_smem_desc(st + L::kOffADense + t * 32, 1024, 16, 2);
-            uint64_t db = ptx::make_smem_desc(st + L::kOffW + t * 32, 1024, 16, 2);
-            ptx::mma_nvf4_dense<1>(tmem_base + L::kColAcc, da, db, idesc_d, tmem_base + L::kColSfaD + 4 * t,
-                                   tmem_base + L::kColSfbD + t * (BN / 32), accumulate);
-            accumulate = 1;
-          }
-        }
-        ptx::tc_commit<1>(empty_bar + s);
       }
-      if (ok) ptx::tc_commit<1>(acc_bar);
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------ epilogue (warps 2..9)
+    const int ew = warp - 2;
     const int quad = warp & 3;  // tensor-memory lane quadrant this warp may read
-    const int row = m_tile * kBM + quad * 32 + lane;
-    bool ok = ptx::mbar_wait(acc_bar, 0, abort_flag);
-    if (!ok) {
-      *abort_flag = 1;
-      atomicExch(p.error_flag, 3);
-    }
-    ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
-      ptx::tc_fence_after();
-      const float alpha = p.alpha_ptr ? p.alpha * (*p.alpha_ptr) : p.alpha;
-      const float beta = p.beta;
-      const bool has_c = (p.c_in != nullptr) && (beta != 0.0f);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t acc[32];
-        ptx::tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(L::kColAcc + c0), acc);
-        ptx::tmem_ld_wait();
-        const int col0 = n_tile * BN + c0;
-        if (row < p.m && col0 < p.n) {
-          const size_t off = (size_t)row * p.n + col0;
-          const bool full = (col0 + 32 <= p.n) && ((p.n & 7) == 0);
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {  // 8 columns per 16-byte store
-            float f[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) f[i] = alpha * __uint_as_float(acc[8 * v + i]);
-            if (has_c) {
-              if (full) {
-                uint4 cv = *reinterpret_cast<const uint4 *>(p.c_in + off + 8 * v);
-                uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  f[2 * i] = __fmaf_rn(beta, bf16_bits_to_float(cw[i] & 0xFFFFu), f[2 * i]);
-                  f[2 * i + 1] = __fmaf_rn(beta, bf16_bits_to_float(cw[i] >> 16), f[2 * i + 1]);
-                }
-              } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                  if (col0 + 8 * v + i < p.n) f[i] = __fmaf_rn(beta, __bfloat162float(p.c_in[off + 8 * v + i]), f[i]);
-              }
-            }
-            uint32_t o[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint32_t lo = float_to_bf16_bits(f[2 * i]), hi = float_to_bf16_bits(f[2 * i + 1]);
-              if (p.bias != nullptr) {
-                // bias is added to the bf16 result, as a separate bf16 add would
-                const int cc = col0 + 8 * v + 2 * i;
-                float b0 = cc < p.n ? __bfloat162float(p.bias[cc]) : 0.0f;
-                float b1 = cc + 1 < p.n ? __bfloat162float(p.bias[cc + 1]) : 0.0f;
-                lo = float_to_bf16_bits(bf16_bits_to_float(lo) + b0);
-                hi = float_to_bf16_bits(bf16_bits_to_float(hi) + b1);
-              }
-              o[i] = lo | (hi << 16);
-            }
-            if (full) {
-              *reinterpret_cast<uint4 *>(p.d + off + 8 * v) = make_uint4(o[0], o[1], o[2], o[3]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 8; ++i)
-                if (col0 + 8 * v + i < p.n)
-                  p.d[off + 8 * v + i] = __ushort_as_bfloat16((unsigned short)((o[i >> 1] >> (16 * (i & 1))) & 0xFFFFu));
-            }
-          }
-        }
+    const int half = ew >> 2;   // which half of the tile's columns
+    const float alpha = p.alpha_ptr ? p.alpha * (*p.alpha_ptr) : p.alpha;
+    const float beta = p.beta;
+    const bool has_c = (p.c_in != nullptr) && (beta != 0.0f);
+    uint32_t tile_iter = 0;
+    for (int u = unit0; u < num_units; u += unit_stride, ++tile_iter) {
+      const int m_tile = PAIR ? 2 * (u % m_units) + (int)cta_rank : (u % m_units);
+      const int n_tile = u / m_units;
+      bool ok = ptx::mbar_wait(acc_full_bar, tile_iter & 1u, abort_flag);
+      if (!ok) {
+        *abort_flag = 1;
+        atomicExch(p.error_flag, 3);
       }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ptx::tc_fence_after();
+      uint32_t acc[kColsPerEpiWarp];
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(L::kColAcc + half * kColsPerEpiWarp);
+#pragma unroll
+      for (int c = 0; c < kColsPerEpiWarp / 32; ++c)
+        ptx::tmem_ld_32x32b_x32(taddr + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&acc[32 * c]));
+      ptx::tmem_ld_wait();
+      // the accumulator is in registers: give tensor memory back before the slow part
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (PAIR && !leader)
+          ptx::mbar_arrive_cluster(acc_empty_bar, 0);
+        else
+          ptx::mbar_arrive(acc_empty_bar);
+      }
+      const int row = m_tile * kBM + quad * 32 + lane;
+      const int col_base = n_tile * BN + half * kColsPerEpiWarp;
+#pragma unroll
+      for (int c = 0; c < kColsPerEpiWarp / 32; ++c)
+        epilogue_chunk(p, &acc[32 * c], row, col_base + 32 * c, alpha, beta, has_c);
     }
   }
 
   ptx::tc_fence_before();
   __syncthreads();
+  if (PAIR) ptx::cluster_sync();  // neither CTA leaves (or frees tensor memory) while its peer may still use it
   if (warp == 1) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc<1>(tmem_base, L::kTmemCols);
+    ptx::tmem_dealloc<CG>(tmem_base, L::kTmemCols);
   }
 }
 
@@ -343,23 +466,46 @@ bool make_tmap_bytes(CUtensorMap *map, const void *base, uint64_t rows, uint64_t
   return r == CUDA_SUCCESS;
 }
 
-template <int BN, bool SPARSE, bool DENSE>
-cudaError_t launch(const GemmArgs &a, cudaStream_t stream) {
-  using L = StageLayout<BN, SPARSE, DENSE>;
-  static bool attr_set[64] = {};
-  auto kernel = gemm_kernel<BN, SPARSE, DENSE>;
+struct DeviceInfo {
+  bool known = false;
+  int sms = 0;
+};
+
+// Per-device state: SM count and which kernel instantiations already have their
+// shared-memory attribute set.
+cudaError_t device_info(int *dev_out, int *sms_out) {
+  static DeviceInfo info[64];
   int dev = 0;
-  cudaError_t de = cudaGetDevice(&dev);
-  if (de != cudaSuccess) return de;
-  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes);
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!info[dev].known) {
+    e = cudaDeviceGetAttribute(&info[dev].sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return e;
-    if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    info[dev].known = true;
+  }
+  *dev_out = dev;
+  *sms_out = info[dev].sms;
+  return cudaSuccess;
+}
+
+template <int BN, bool SPARSE, bool DENSE, bool PAIR>
+cudaError_t launch(const GemmArgs &a, cudaStream_t stream) {
+  using L = StageLayout<BN, SPARSE, DENSE, PAIR>;
+  static bool attr_set[64] = {};
+  auto kernel = gemm_kernel<BN, SPARSE, DENSE, PAIR>;
+  int dev = 0, sms = 0;
+  cudaError_t e = device_info(&dev, &sms);
+  if (e != cudaSuccess) return e;
+  if (!attr_set[dev]) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
   }
   CUtensorMap tm_w, tm_ad, tm_ac;
   memset(&tm_ad, 0, sizeof(tm_ad));
   memset(&tm_ac, 0, sizeof(tm_ac));
-  if (!make_tmap_bytes(&tm_w, a.b, (uint64_t)a.n, (uint64_t)a.k / 2, BN, 128, CU_TENSOR_MAP_SWIZZLE_128B))
+  if (!make_tmap_bytes(&tm_w, a.b, (uint64_t)a.n, (uint64_t)a.k / 2, L::kWRows, 128, CU_TENSOR_MAP_SWIZZLE_128B))
     return cudaErrorInvalidValue;
   if (DENSE && !make_tmap_bytes(&tm_ad, a.a_dense, (uint64_t)a.m, (uint64_t)a.k / 2, kBM, 128, CU_TENSOR_MAP_SWIZZLE_128B))
     return cudaErrorInvalidValue;
@@ -381,9 +527,27 @@ cudaError_t launch(const GemmArgs &a, cudaStream_t stream) {
   p.n = a.n;
   p.k = a.k;
   p.error_flag = a.error_flag;
-  dim3 grid((a.n + BN - 1) / BN, (a.m + kBM - 1) / kBM);
-  kernel<<<grid, kGemmThreads, L::kSmemBytes, stream>>>(tm_w, tm_ad, tm_ac, p);
-  return cudaGetLastError();
+  const int n_tiles = (a.n + BN - 1) / BN;
+  const int m_units = PAIR ? (a.m + 255) / 256 : (a.m + kBM - 1) / kBM;
+  const int units = m_units * n_tiles;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  if (PAIR) {
+    const int clusters = units < sms / 2 ? units : sms / 2;
+    cfg.gridDim = dim3(2 * clusters);
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  } else {
+    cfg.gridDim = dim3(units < sms ? units : sms);
+  }
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = L::kSmemBytes;
+  cfg.stream = stream;
+  return cudaLaunchKernelEx(&cfg, kernel, tm_w, tm_ad, tm_ac, p);
 }
 
 }  // namespace
@@ -392,15 +556,22 @@ cudaError_t run_gemm(const GemmArgs &a, cudaStream_t stream) {
   const bool sparse = a.a_comp != nullptr;
   const bool dense = a.a_dense != nullptr;
   if (!sparse && !dense) return cudaErrorInvalidValue;
-  const int bn = a.tile_n == 128 ? 128 : (a.tile_n == 256 ? 256 : (a.n % 256 == 0 && a.m > 128 ? 256 : 128));
-  if (bn == 256) {
-    if (sparse && dense) return launch<256, true, true>(a, stream);
-    if (sparse) return launch<256, true, false>(a, stream);
-    return launch<256, false, true>(a, stream);
+  // tile_n: 0 = automatic, 128 / 256 = single-CTA tiles of that width, 512 = CTA pairs (256 x 256)
+  const bool pair = a.tile_n == 512 || (a.tile_n == 0 && a.m > 128 && a.n > 128);
+  if (pair) {
+    if (sparse && dense) return launch<256, true, true, true>(a, stream);
+    if (sparse) return launch<256, true, false, true>(a, stream);
+    return launch<256, false, true, true>(a, stream);
   }
-  if (sparse && dense) return launch<128, true, true>(a, stream);
-  if (sparse) return launch<128, true, false>(a, stream);
-  return launch<128, false, true>(a, stream);
+  const int bn = a.tile_n == 128 ? 128 : (a.tile_n == 256 ? 256 : (a.n > 128 ? 256 : 128));
+  if (bn == 256) {
+    if (sparse && dense) return launch<256, true, true, false>(a, stream);
+    if (sparse) return launch<256, true, false, false>(a, stream);
+    return launch<256, false, true, false>(a, stream);
+  }
+  if (sparse && dense) return launch<128, true, true, false>(a, stream);
+  if (sparse) return launch<128, true, false, false>(a, stream);
+  return launch<128, false, true, false>(a, stream);
 }
 
 }  // namespace sharq

@@ -49,7 +49,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint64_t *bar, uint32_t cta_
       "{\n\t"
       ".reg .b32 remote;\n\t"
       "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
-      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remote];\n\t"
+      "mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [remote];\n\t"
       "}" ::"r"(smem_u32(bar)),
       "r"(cta_rank)
       : "memory");
@@ -79,6 +79,43 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     if (*abort_flag != 0) return false;
     if (clock64() - start > kWaitLimitCycles) return false;
   }
+}
+
+// Same, with acquire semantics at cluster scope: for barriers that another CTA of the
+// cluster arrives on.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.relaxed.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long start = clock64();
+  while (true) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (*abort_flag != 0) return false;
+    if (clock64() - start > kWaitLimitCycles) return false;
+  }
+}
+
+// ---------------------------------------------------------------- clusters
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 // ---------------------------------------------------------------- TMA

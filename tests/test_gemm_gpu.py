@@ -33,7 +33,7 @@ def _to_np(t):
     return t.float().cpu().numpy()
 
 
-@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("tile_n", [128, 256, 512])
 @pytest.mark.parametrize("m,n,k", SHAPES)
 def test_dense_sparse_fused(oracle, m, n, k, tile_n):
     from sharq_b200 import ops
