@@ -7,12 +7,23 @@
 //   kernels/src/bindings.cpp:270-274,320-326,337        (zero fills and the tensor-scale glue)
 // and the host-side amax / divide passes of model/quantize.py:179-183.
 //
-// Work split: one thread owns one 32-element group (one sparse scale, two residual
-// scales).  A warp covers 4 rows x 8 groups = 4 rows x 256 columns, which makes its
-// metadata (4 rows x 16 B) and its packed outputs contiguous per row; a CTA of 8 warps
-// covers 32 rows x 256 columns.  Every byte of every output buffer is written by the
-// kernel (payload by its owner thread, padding rows/columns and the spare tail of
-// each buffer with zeros), so callers may hand in uninitialised memory.
+// Work split of the prepare kernel: one thread owns one 32-element group (one sparse scale,
+// two residual scales).  A warp covers 4 rows x 8 groups = 4 rows x 256 columns, which makes
+// its metadata (4 rows x 16 B) and its packed outputs contiguous per row; a CTA of 8 warps
+// covers 32 rows x 256 columns.  Every byte of every output buffer is written by the kernel
+// (payload by its owner thread, padding rows/columns and the spare tail of each buffer with
+// zeros), so callers may hand in uninitialised memory.
+//
+// The kernel is instruction-bound, so the arithmetic is arranged to need few instructions
+// while producing exactly the reference's bits:
+//   * pair selection on integer keys: the pair score max(|a|,|b|) of two bf16-exact values
+//     has 16 zero low bits as a float, so `bits | (3 - pair)` is a key whose integer order is
+//     "larger score first, earlier pair first" - the reference's strict-'>' scan order;
+//   * scale value and reciprocal of the 126 possible UE4M3 codes come from a shared-memory
+//     table filled with ue4m3 -> float and the IEEE reciprocal;
+//   * e2m1 encode/decode use the hardware conversions; x - q*s is one FMA (q*s is exact);
+//   * x / scale (tensor scale) is y * (1/scale) when that product is provably on the same side
+//     of every bf16 rounding boundary as the IEEE quotient, and an IEEE division otherwise.
 #include "common.cuh"
 #include "prepare.cuh"
 
@@ -27,95 +38,147 @@ constexpr int kRowsPerCta = kRowsPerWarp * kWarpsPerCta;  // 32
 constexpr int kColsPerCta = kGroupsPerWarp * 32;          // 256
 constexpr int kPrepareThreads = 32 * kWarpsPerCta;
 
-// Read-only 16-byte load that allocates in L1: a lane reads its 64-byte group with four
-// of these and the second load of each 32-byte sector is served by L1.
-__device__ __forceinline__ uint4 ld_nc_16(const void *p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }
+__device__ __forceinline__ float lo_f(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float hi_f(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
 
-__device__ __forceinline__ uint4 ld_ca_16(const void *p) {
-  return *reinterpret_cast<const uint4 *>(p);
+// two floats -> packed bf16x2 (a in the low half), round to nearest even
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+
+// Raise the tensor absmax (non-negative float bits, integer order = float order).  The read
+// first keeps the number of same-address atomics small once the maximum has settled.
+__device__ __forceinline__ void raise_amax(unsigned int *amax_bits, float mx) {
+  const unsigned int bits = __float_as_uint(mx);
+  if (bits > *reinterpret_cast<volatile unsigned int *>(amax_bits)) atomicMax(amax_bits, bits);
 }
 
 // ---------------------------------------------------------------------------
-// Row statistics.
-//   mode kRms : inv_rms[r] = rsqrtf(sum(x^2)/K + eps) with the reference's summation
-//               order (each 32-group left to right, then the group sums left to
-//               right), and the tensor-wide max of |bf16(x * inv_rms * gamma)|.
-//   mode kAbs : only the tensor-wide max of |x|.
-// The tensor max is accumulated with an integer atomicMax on the float bits (all
-// candidates are non-negative).  One warp per row.
+// Row statistics for the RMSNorm path, one CTA per row, one thread per 32-element group:
+//   inv_rms[r] = rsqrtf(sum(x^2)/K + eps) with the reference's summation order (each group
+//   left to right - an FMA chain whose products are exact - then the group sums left to
+//   right by one thread), and the tensor-wide max of |bf16(x * inv_rms * gamma)|.
+// Many rows are resident per SM, so the serial sums of different rows overlap.
 // ---------------------------------------------------------------------------
-template <bool kRms>
-__global__ void __launch_bounds__(256) row_stats_kernel(const __nv_bfloat16 *__restrict__ x,
-                                                         const __nv_bfloat16 *__restrict__ gamma, float eps,
-                                                         int m, int k, float *__restrict__ inv_rms,
-                                                         unsigned int *__restrict__ amax_bits) {
-  extern __shared__ float partial[];  // [warps][k/32]
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+__global__ void __launch_bounds__(1024, 2) rms_stats_kernel(const __nv_bfloat16 *__restrict__ x,
+                                                          const __nv_bfloat16 *__restrict__ gamma, float eps, int k,
+                                                          float *__restrict__ inv_rms,
+                                                          unsigned int *__restrict__ amax_bits) {
+  extern __shared__ float partial[];  // [k/32] group sums, then [0] is reused for inv_rms
+  __shared__ float warp_max[32];
   const int groups = k >> 5;
-  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (row >= m) return;
-  const __nv_bfloat16 *xr = x + (size_t)row * k;
-  float inv = 1.0f;
-  float mx = 0.0f;
-
-  if (kRms) {
-    float *my = partial + (size_t)warp * groups;
-    for (int g = lane; g < groups; g += 32) {
-      const uint4 *p = reinterpret_cast<const uint4 *>(xr + (size_t)g * 32);
-      float s = 0.0f;
+  const int g = threadIdx.x;
+  const int row = blockIdx.x;
+  const bool live = g < groups;
+  uint32_t w[16];
+  if (live) {
+    const uint4 *src = reinterpret_cast<const uint4 *>(x + (size_t)row * k + (size_t)g * 32);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint4 v = ld_ca_16(p + j);
-        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    for (int j = 0; j < 4; ++j) {
+      uint4 v = __ldg(src + j);
+      w[4 * j + 0] = v.x;
+      w[4 * j + 1] = v.y;
+      w[4 * j + 2] = v.z;
+      w[4 * j + 3] = v.w;
+    }
+    float s = 0.0f;
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          float a = bf16_bits_to_float(w[t] & 0xFFFFu);
-          float b = bf16_bits_to_float(w[t] >> 16);
-          s = __fmaf_rn(a, a, s);  // a*a is exact in float, so this equals s + a*a
-          s = __fmaf_rn(b, b, s);
-        }
-      }
-      my[g] = s;
+    for (int i = 0; i < 16; ++i) {
+      float a = lo_f(w[i]), b = hi_f(w[i]);
+      s = __fmaf_rn(a, a, s);  // a*a is exact in float, so this equals s + a*a
+      s = __fmaf_rn(b, b, s);
     }
-    __syncwarp();
-    float total = 0.0f;
-    if (lane == 0) {
-      for (int g = 0; g < groups; ++g) total = __fadd_rn(total, my[g]);
-      inv = rsqrtf(__fadd_rn(__fdiv_rn(total, (float)k), eps));
-      inv_rms[row] = inv;
-    }
-    inv = __shfl_sync(0xffffffffu, inv, 0);
+    partial[g] = s;
   }
-
-  for (int c = lane; c < (k >> 3); c += 32) {
-    uint4 v = ld_ca_16(reinterpret_cast<const uint4 *>(xr) + c);
-    uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    if (kRms) {
-      uint4 gv = *(reinterpret_cast<const uint4 *>(gamma) + c);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float total = 0.0f;
+    for (int i = 0; i < groups; i += 4) {  // groups is a multiple of 4 (K % 128 == 0)
+      float4 v = *reinterpret_cast<const float4 *>(partial + i);
+      total = __fadd_rn(total, v.x);
+      total = __fadd_rn(total, v.y);
+      total = __fadd_rn(total, v.z);
+      total = __fadd_rn(total, v.w);
+    }
+    float inv = rsqrtf(__fadd_rn(__fdiv_rn(total, (float)k), eps));
+    inv_rms[row] = inv;
+    warp_max[31] = inv;  // slot 31 is free: at most 32 warps, reduction uses [0, nwarps)
+  }
+  __syncthreads();
+  const float inv = warp_max[31];
+  __syncthreads();
+  float mx = 0.0f;
+  if (live) {
+    const uint4 *gsrc = reinterpret_cast<const uint4 *>(gamma + (size_t)g * 32);
+    __nv_bfloat162 m2 = __floats2bfloat162_rn(0.0f, 0.0f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 gv = __ldg(gsrc + j);
       uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
-        float a = __fmul_rn(__fmul_rn(bf16_bits_to_float(w[t] & 0xFFFFu), inv), bf16_bits_to_float(gw[t] & 0xFFFFu));
-        float b = __fmul_rn(__fmul_rn(bf16_bits_to_float(w[t] >> 16), inv), bf16_bits_to_float(gw[t] >> 16));
-        mx = fmaxf(mx, fabsf(bf16_bits_to_float(float_to_bf16_bits(a))));
-        mx = fmaxf(mx, fabsf(bf16_bits_to_float(float_to_bf16_bits(b))));
-      }
-    } else {
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        mx = fmaxf(mx, fabsf(bf16_bits_to_float(w[t] & 0xFFFFu)));
-        mx = fmaxf(mx, fabsf(bf16_bits_to_float(w[t] >> 16)));
+        float a = __fmul_rn(__fmul_rn(lo_f(w[4 * j + t]), inv), lo_f(gw[t]));
+        float b = __fmul_rn(__fmul_rn(hi_f(w[4 * j + t]), inv), hi_f(gw[t]));
+        m2 = __hmax2(m2, __habs2(__floats2bfloat162_rn(a, b)));
       }
     }
+    mx = fmaxf(__bfloat162float(m2.x), __bfloat162float(m2.y));
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  if (lane == 0) atomicMax(amax_bits, __float_as_uint(mx));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = (blockDim.x + 31) >> 5;
+  if (lane == 0) warp_max[warp] = mx;
+  __syncthreads();
+  if (warp == 0) {
+    mx = lane < nwarps ? warp_max[lane] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) raise_amax(amax_bits, mx);
+  }
+}
+
+// Tensor-wide max |x| of a bf16 tensor (non-RMSNorm path): flat grid-stride reduction.
+__global__ void __launch_bounds__(256) abs_stats_kernel(const __nv_bfloat16 *__restrict__ x, size_t n16,
+                                                         unsigned int *__restrict__ amax_bits) {
+  __shared__ float warp_max[8];
+  __nv_bfloat162 m2 = __floats2bfloat162_rn(0.0f, 0.0f);
+  const uint4 *src = reinterpret_cast<const uint4 *>(x);
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = (i + u * stride < n16) ? __ldg(src + i + u * stride) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      m2 = __hmax2(m2, __habs2(*reinterpret_cast<__nv_bfloat162 *>(&v[u].x)));
+      m2 = __hmax2(m2, __habs2(*reinterpret_cast<__nv_bfloat162 *>(&v[u].y)));
+      m2 = __hmax2(m2, __habs2(*reinterpret_cast<__nv_bfloat162 *>(&v[u].z)));
+      m2 = __hmax2(m2, __habs2(*reinterpret_cast<__nv_bfloat162 *>(&v[u].w)));
+    }
+  }
+  float mx = fmaxf(__bfloat162float(m2.x), __bfloat162float(m2.y));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) warp_max[warp] = mx;
+  __syncthreads();
+  if (warp == 0) {
+    mx = lane < 8 ? warp_max[lane] : 0.0f;
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) raise_amax(amax_bits, mx);
+  }
 }
 
 // ---------------------------------------------------------------------------
 // The 32-element group: selection, sparse quantisation, residual quantisation.
 // ---------------------------------------------------------------------------
+struct ScaleTables {
+  float value[128];  // ue4m3 code -> float
+  float recip[128];  // IEEE 1.0f / value
+};
+
 struct GroupOut {
   uint32_t q_res[4];     // 16 B dense residual payload
   uint32_t a_comp[2];    // 8 B compressed sparse payload
@@ -125,81 +188,83 @@ struct GroupOut {
   uint32_t sf_res;       // 2 B (first 16-group in the low byte)
 };
 
-__device__ __forceinline__ float scale_from_max(float mx, uint32_t &code) {
-  float s = clamp_val(__fdiv_rn(mx, kFp4Max), kScaleEps, kFp8Max);
-  code = float_to_ue4m3(s);
-  return ue4m3_to_float(code);
+// four packed e2m1x2 bytes -> four half2 words (element 2i of byte i in the low half)
+__device__ __forceinline__ void decode_e2m1x8(uint32_t word, uint32_t (&h)[4]) {
+  asm("{\n\t"
+      ".reg .b8 b0, b1, b2, b3;\n\t"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t"
+      "}"
+      : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+      : "r"(word));
+}
+
+__device__ __forceinline__ uint32_t scale_code_from_max(float mx) {
+  return float_to_ue4m3(clamp_val(__fdiv_rn(mx, kFp4Max), kScaleEps, kFp8Max));
 }
 
 template <bool kDebug>
-__device__ __forceinline__ void quantize_group32(float (&x)[32], GroupOut &o) {
-  // -- pair selection per 8-element chunk (strict '>' : the earlier pair wins ties)
-  uint32_t keep_pairs = 0;  // bit (4*chunk + pair)
+__device__ __forceinline__ void quantize_group32(const uint32_t (&xw)[16], const ScaleTables &tbl, GroupOut &o) {
+  float x[32];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    x[2 * i] = lo_f(xw[i]);
+    x[2 * i + 1] = hi_f(xw[i]);
+  }
+
+  // -- pair selection per 8-element chunk on integer keys
+  uint32_t lo_idx[4], hi_idx[4];
+  uint32_t max_key = 0;
   uint32_t meta = 0;
-  uint32_t sel[4];          // idx0 | idx1 << 2 per chunk
-  float sparse_max = 0.0f;
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    float best0 = -1.0f, best1 = -1.0f;
-    int i0 = 0, i1 = 1;
+    uint32_t key[4];
 #pragma unroll
-    for (int p = 0; p < 4; ++p) {
-      float score = fmaxf(fabsf(x[8 * c + 2 * p]), fabsf(x[8 * c + 2 * p + 1]));
-      bool gt0 = score > best0;
-      bool gt1 = score > best1;
-      // order of updates mirrors: if (gt0) {best1=best0; i1=i0; best0=score; i0=p;} else if (gt1) {best1=score; i1=p;}
-      best1 = gt0 ? best0 : (gt1 ? score : best1);
-      i1 = gt0 ? i0 : (gt1 ? p : i1);
-      best0 = gt0 ? score : best0;
-      i0 = gt0 ? p : i0;
-    }
-    int lo = min(i0, i1), hi = max(i0, i1);
-    sel[c] = (uint32_t)(lo | (hi << 2));
-    meta |= sel[c] << (4 * c);
-    keep_pairs |= ((1u << lo) | (1u << hi)) << (4 * c);
-    // best0/best1 are the two kept pair scores, so their max is the kept absmax
-    sparse_max = fmaxf(sparse_max, fmaxf(best0, best1));
+    for (int p = 0; p < 4; ++p)
+      key[p] = __float_as_uint(fmaxf(fabsf(x[8 * c + 2 * p]), fabsf(x[8 * c + 2 * p + 1]))) | (uint32_t)(3 - p);
+    const uint32_t m01 = max(key[0], key[1]), n01 = min(key[0], key[1]);
+    const uint32_t m23 = max(key[2], key[3]), n23 = min(key[2], key[3]);
+    const uint32_t best = max(m01, m23);
+    const uint32_t second = max(min(m01, m23), max(n01, n23));
+    const uint32_t ib = 3u - (best & 3u), is = 3u - (second & 3u);
+    lo_idx[c] = min(ib, is);
+    hi_idx[c] = max(ib, is);
+    meta |= (lo_idx[c] | (hi_idx[c] << 2)) << (4 * c);
+    max_key = max(max_key, best);
   }
   o.meta = meta;
 
   // -- sparse main path scale (one UE4M3 per 32 logical elements)
-  uint32_t s_code;
-  float s_q = scale_from_max(sparse_max, s_code);
-  float s_r = __frcp_rn(s_q);
+  const uint32_t s_code = scale_code_from_max(__uint_as_float(max_key & 0xFFFF0000u));
+  const float s_q = tbl.value[s_code];
+  const float s_r = tbl.recip[s_code];
   o.sf_sparse = s_code;
-  float half_s = 0.5f * s_q;  // exact
 
-  // -- quantise every pair, keep the selected ones, form the residual
+  // -- quantise every pair, mask to the selected ones, form the residual
   float r[32];
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    // the 4 pair-bytes of this chunk: quantise all 8 values, then mask to the kept pairs
-    uint32_t all4 = pack_e2m1x8(__fmul_rn(x[8 * c + 0], s_r), __fmul_rn(x[8 * c + 1], s_r),
-                                __fmul_rn(x[8 * c + 2], s_r), __fmul_rn(x[8 * c + 3], s_r),
-                                __fmul_rn(x[8 * c + 4], s_r), __fmul_rn(x[8 * c + 5], s_r),
-                                __fmul_rn(x[8 * c + 6], s_r), __fmul_rn(x[8 * c + 7], s_r));
-    uint32_t dense4 = 0;
+    const uint32_t all4 = pack_e2m1x8(__fmul_rn(x[8 * c + 0], s_r), __fmul_rn(x[8 * c + 1], s_r),
+                                      __fmul_rn(x[8 * c + 2], s_r), __fmul_rn(x[8 * c + 3], s_r),
+                                      __fmul_rn(x[8 * c + 4], s_r), __fmul_rn(x[8 * c + 5], s_r),
+                                      __fmul_rn(x[8 * c + 6], s_r), __fmul_rn(x[8 * c + 7], s_r));
+    const uint32_t mask4 = (0xFFu << (8 * lo_idx[c])) | (0xFFu << (8 * hi_idx[c]));
+    const uint32_t dense4 = all4 & mask4;  // dropped pairs become +0,+0: their residual is x itself
+    if (kDebug) o.q_sparse[c] = dense4;
+    uint32_t h[4];
+    decode_e2m1x8(dense4, h);
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
-      const int i = 8 * c + 2 * p;
-      bool keep = (keep_pairs >> (4 * c + p)) & 1u;
-      uint32_t byte = (all4 >> (8 * p)) & 0xFFu;
-      float d0 = (float)e2m1_twice_magnitude(byte);
-      float d1 = (float)e2m1_twice_magnitude(byte >> 4);
-      d0 = (byte & 0x08u) ? -d0 : d0;
-      d1 = (byte & 0x80u) ? -d1 : d1;
-      // x - q*s with q*s = d * (s/2) exact, single rounding
-      float r0 = __fmaf_rn(-d0, half_s, x[i]);
-      float r1 = __fmaf_rn(-d1, half_s, x[i + 1]);
-      r[i] = keep ? r0 : x[i];
-      r[i + 1] = keep ? r1 : x[i + 1];
-      dense4 |= keep ? (0xFFu << (8 * p)) : 0u;
+      const float2 q = __half22float2(*reinterpret_cast<__half2 *>(&h[p]));
+      // q * s_q is exact (2-bit x 4-bit significands), so the FMA rounds once like x - (q*s)
+      r[8 * c + 2 * p] = __fmaf_rn(-q.x, s_q, x[8 * c + 2 * p]);
+      r[8 * c + 2 * p + 1] = __fmaf_rn(-q.y, s_q, x[8 * c + 2 * p + 1]);
     }
-    dense4 &= all4;
-    if (kDebug) o.q_sparse[c] = dense4;
-    uint32_t b0 = (dense4 >> (8 * (sel[c] & 3u))) & 0xFFu;
-    uint32_t b1 = (dense4 >> (8 * (sel[c] >> 2))) & 0xFFu;
-    uint32_t two = b0 | (b1 << 8);
+    // the two kept pair-bytes, ascending pair order
+    const uint32_t two = __byte_perm(dense4, 0u, lo_idx[c] | (hi_idx[c] << 4) | 0x4400u);
     if (c & 1)
       o.a_comp[c >> 1] |= two << 16;
     else
@@ -213,20 +278,33 @@ __device__ __forceinline__ void quantize_group32(float (&x)[32], GroupOut &o) {
     float mx = 0.0f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) mx = fmaxf(mx, fabsf(r[16 * h + i]));
-    uint32_t code;
-    float rq = scale_from_max(mx, code);
-    float rr = __frcp_rn(rq);
+    const uint32_t code = scale_code_from_max(mx);
+    const float rr = tbl.recip[code];
     sf_res |= code << (8 * h);
 #pragma unroll
     for (int wv = 0; wv < 2; ++wv) {
       const int i = 16 * h + 8 * wv;
-      uint32_t word = pack_e2m1x8(__fmul_rn(r[i + 0], rr), __fmul_rn(r[i + 1], rr), __fmul_rn(r[i + 2], rr),
-                                  __fmul_rn(r[i + 3], rr), __fmul_rn(r[i + 4], rr), __fmul_rn(r[i + 5], rr),
-                                  __fmul_rn(r[i + 6], rr), __fmul_rn(r[i + 7], rr));
-      o.q_res[2 * h + wv] = word;
+      o.q_res[2 * h + wv] =
+          pack_e2m1x8(__fmul_rn(r[i + 0], rr), __fmul_rn(r[i + 1], rr), __fmul_rn(r[i + 2], rr), __fmul_rn(r[i + 3], rr),
+                      __fmul_rn(r[i + 4], rr), __fmul_rn(r[i + 5], rr), __fmul_rn(r[i + 6], rr), __fmul_rn(r[i + 7], rr));
     }
   }
   o.sf_res = sf_res;
+}
+
+// bf16(y / scale) for the two halves of a packed word, y already bf16-exact floats.
+// q = y * recip is within 2 ulp of the true quotient; when q is more than 4 ulp away from
+// every bf16 rounding boundary (low 16 bits == 0x8000) the IEEE quotient rounds to the same
+// bf16 value, otherwise the IEEE division is used.
+__device__ __forceinline__ uint32_t scaled_bf16x2(float ya, float yb, float scale, float recip) {
+  float qa = __fmul_rn(ya, recip), qb = __fmul_rn(yb, recip);
+  const uint32_t ta = (__float_as_uint(qa) + 0x8004u) & 0xFFFFu;
+  const uint32_t tb = (__float_as_uint(qb) + 0x8004u) & 0xFFFFu;
+  if (ta < 9u || tb < 9u) {
+    qa = __fdiv_rn(ya, scale);
+    qb = __fdiv_rn(yb, scale);
+  }
+  return pack_bf16x2(qa, qb);
 }
 
 // ---------------------------------------------------------------------------
@@ -234,8 +312,8 @@ __device__ __forceinline__ void quantize_group32(float (&x)[32], GroupOut &o) {
 //   kMode 0: input already scaled (drop-in for fused_sparse_residual_quantize_x)
 //   kMode 1: RMSNorm + tensor scale inline (needs inv_rms and the tensor absmax)
 //   kMode 2: tensor scale inline only (x / scale rounded to bf16), scale from absmax
-// grid.x = K tiles of 256 columns, grid.y = row tiles of 32 rows up to ceil128(M),
-// plus kTailCtas extra CTAs in grid.y that zero the spare tail of each buffer.
+// Persistent: a fixed number of CTAs per SM loops over 32-row x 256-column tiles (rows up to
+// ceil128(M)); every CTA first helps zero the spare tail of each buffer.
 // ---------------------------------------------------------------------------
 struct PrepareParams {
   const __nv_bfloat16 *x;
@@ -253,7 +331,7 @@ struct PrepareParams {
   int row_tiles;  // ceil128(m) / 32
 };
 
-constexpr int kTailCtas = 4;
+constexpr int kPrepareCtasPerSm = 3;
 
 __device__ __forceinline__ void zero_range(uint8_t *base, size_t begin, size_t end, int worker, int workers) {
   if (base == nullptr || begin >= end) return;
@@ -268,119 +346,142 @@ __device__ __forceinline__ void zero_range(uint8_t *base, size_t begin, size_t e
 }
 
 template <int kMode, bool kDebug>
-__global__ void __launch_bounds__(kPrepareThreads) prepare_kernel(const PrepareParams p) {
+__global__ void __launch_bounds__(kPrepareThreads, kPrepareCtasPerSm) prepare_kernel(const PrepareParams p) {
   const int m = p.m, k = p.k;
   const int groups32 = k >> 5;
   const int aligned_m = (m + 127) / 128 * 128;
 
-  if ((int)blockIdx.y >= p.row_tiles) {
-    // tail CTAs: zero what no owner thread writes
-    const int worker = ((int)blockIdx.y - p.row_tiles) * gridDim.x * blockDim.x + blockIdx.x * blockDim.x + threadIdx.x;
-    const int workers = kTailCtas * gridDim.x * blockDim.x;
+  __shared__ ScaleTables tbl;
+  if (threadIdx.x < 128) {
+    const float v = ue4m3_to_float(threadIdx.x);
+    tbl.value[threadIdx.x] = v;
+    tbl.recip[threadIdx.x] = __frcp_rn(v);  // code 0 is never looked up (scales are clamped to >= 2^-9)
+  }
+  __syncthreads();
+
+  // zero what no owner thread writes: the spare tail of the scale buffers and of A_comp
+  {
+    const int worker = blockIdx.x * blockDim.x + threadIdx.x;
+    const int workers = gridDim.x * blockDim.x;
     const size_t bands = (size_t)aligned_m / 128;
     zero_range(p.sfa_sparse, bands * (size_t)(groups32 / 4) * 512, sf_alloc_bytes(m, k), worker, workers);
     zero_range(p.sf_res, bands * (size_t)(k / 16 / 4) * 512, sf_alloc_bytes(m, k), worker, workers);
     if (!kDebug) zero_range(p.a_comp, (size_t)m * (k / 4), a_comp_bytes(m, k), worker, workers);
-    return;
+  }
+
+  float scale = 1.0f, recip = 1.0f;
+  if (kMode != 0) {
+    const float amax = __uint_as_float(*p.amax_bits);
+    // ATen divides a CUDA tensor by a host scalar by multiplying with the float
+    // reciprocal; clamp(min=1e-9) follows (kernels/src/bindings.cpp:337 of the reference).
+    scale = fmaxf(__fmul_rn(amax, 1.0f / 2688.0f), 1.0e-9f);
+    recip = __frcp_rn(scale);
+    if (p.scale_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *p.scale_out = scale;
   }
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = blockIdx.y * kRowsPerCta + warp * kRowsPerWarp + (lane >> 3);
-  const int group = blockIdx.x * kGroupsPerWarp + (lane & 7);
-  const bool row_ok = row < m;
-  const bool col_ok = group < groups32;
-  const bool live = row_ok && col_ok;
+  const int k_tiles = (k + kColsPerCta - 1) / kColsPerCta;
+  const int total_tiles = k_tiles * p.row_tiles;
+  const int row_in_tile = warp * kRowsPerWarp + (lane >> 3);
+  const int group_in_tile = lane & 7;
 
-  GroupOut o;
-  o.a_comp[0] = o.a_comp[1] = 0;
-  o.meta = 0;
-  o.sf_sparse = 0;
-  o.sf_res = 0;
+  // persistent loop over 32-row x 256-column tiles; the next tile's 64 bytes are loaded
+  // before the current tile is processed, so the loads overlap the arithmetic
+  uint4 next[4];
+  auto issue_loads = [&](int tile) {
+    const int row = (tile / k_tiles) * kRowsPerCta + row_in_tile;
+    const int group = (tile % k_tiles) * kGroupsPerWarp + group_in_tile;
+    if (tile < total_tiles && row < m && group < groups32) {
+      const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (size_t)row * k + (size_t)group * 32);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) o.q_res[i] = o.q_sparse[i] = 0;
-
-  if (live) {
-    float x[32];
-    const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (size_t)row * k + (size_t)group * 32);
-    uint4 v[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = ld_nc_16(src + j);
-
-    float inv = 1.0f, scale = 1.0f;
-    if (kMode != 0) {
-      float amax = __uint_as_float(*p.amax_bits);
-      // ATen divides a CUDA tensor by a host scalar by multiplying with the float
-      // reciprocal; clamp(min=1e-9) follows (kernels/src/bindings.cpp:337 of the reference).
-      scale = fmaxf(__fmul_rn(amax, 1.0f / 2688.0f), 1.0e-9f);
-      if (p.scale_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *p.scale_out = scale;
+      for (int j = 0; j < 4; ++j) next[j] = __ldg(src + j);
     }
-    if (kMode == 1) inv = p.inv_rms[row];
+  };
+  issue_loads(blockIdx.x);
 
+  for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    const int k_tile = tile % k_tiles;
+    const int row = (tile / k_tiles) * kRowsPerCta + row_in_tile;
+    const int group = k_tile * kGroupsPerWarp + group_in_tile;
+    const bool col_ok = group < groups32;
+    const bool live = row < m && col_ok;
+
+    uint32_t xw[16];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-      uint32_t gw[4] = {0, 0, 0, 0};
-      if (kMode == 1) {
-        uint4 gv = *(reinterpret_cast<const uint4 *>(p.gamma + (size_t)group * 32) + j);
-        gw[0] = gv.x; gw[1] = gv.y; gw[2] = gv.z; gw[3] = gv.w;
-      }
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        float a = bf16_bits_to_float(w[t] & 0xFFFFu);
-        float b = bf16_bits_to_float(w[t] >> 16);
-        if (kMode == 1) {
-          a = __fmul_rn(__fmul_rn(a, inv), bf16_bits_to_float(gw[t] & 0xFFFFu));
-          b = __fmul_rn(__fmul_rn(b, inv), bf16_bits_to_float(gw[t] >> 16));
-          a = bf16_bits_to_float(float_to_bf16_bits(a));
-          b = bf16_bits_to_float(float_to_bf16_bits(b));
-        }
-        if (kMode != 0) {
-          a = bf16_bits_to_float(float_to_bf16_bits(__fdiv_rn(a, scale)));
-          b = bf16_bits_to_float(float_to_bf16_bits(__fdiv_rn(b, scale)));
-        }
-        x[8 * j + 2 * t] = a;
-        x[8 * j + 2 * t + 1] = b;
-      }
+      xw[4 * j + 0] = next[j].x;
+      xw[4 * j + 1] = next[j].y;
+      xw[4 * j + 2] = next[j].z;
+      xw[4 * j + 3] = next[j].w;
     }
-    quantize_group32<kDebug>(x, o);
-  }
+    issue_loads(tile + gridDim.x);
 
-  // ---- stores
-  if (live) {
-    uint4 q = make_uint4(o.q_res[0], o.q_res[1], o.q_res[2], o.q_res[3]);
-    *reinterpret_cast<uint4 *>(p.q_res + (size_t)row * (k / 2) + (size_t)group * 16) = q;
-    if (kDebug) {
-      uint4 qs = make_uint4(o.q_sparse[0], o.q_sparse[1], o.q_sparse[2], o.q_sparse[3]);
-      *reinterpret_cast<uint4 *>(p.q_sparse_dense + (size_t)row * (k / 2) + (size_t)group * 16) = qs;
-    } else {
-      *reinterpret_cast<uint2 *>(p.a_comp + (size_t)row * (k / 4) + (size_t)group * 8) = make_uint2(o.a_comp[0], o.a_comp[1]);
+    GroupOut o;
+    o.a_comp[0] = o.a_comp[1] = 0;
+    o.meta = 0;
+    o.sf_sparse = 0;
+    o.sf_res = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o.q_res[i] = o.q_sparse[i] = 0;
+
+    if (live) {
+      if (kMode == 1) {
+        const float inv = p.inv_rms[row];
+        const uint4 *gsrc = reinterpret_cast<const uint4 *>(p.gamma + (size_t)group * 32);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 gv = __ldg(gsrc + j);
+          uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const uint32_t w = xw[4 * j + t];
+            const float a = __fmul_rn(__fmul_rn(lo_f(w), inv), lo_f(gw[t]));
+            const float b = __fmul_rn(__fmul_rn(hi_f(w), inv), hi_f(gw[t]));
+            const uint32_t y = pack_bf16x2(a, b);
+            xw[4 * j + t] = scaled_bf16x2(lo_f(y), hi_f(y), scale, recip);
+          }
+        }
+      } else if (kMode == 2) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) xw[i] = scaled_bf16x2(lo_f(xw[i]), hi_f(xw[i]), scale, recip);
+      }
+      quantize_group32<kDebug>(xw, tbl, o);
+
+      uint4 q = make_uint4(o.q_res[0], o.q_res[1], o.q_res[2], o.q_res[3]);
+      *reinterpret_cast<uint4 *>(p.q_res + (size_t)row * (k / 2) + (size_t)group * 16) = q;
+      if (kDebug) {
+        uint4 qs = make_uint4(o.q_sparse[0], o.q_sparse[1], o.q_sparse[2], o.q_sparse[3]);
+        *reinterpret_cast<uint4 *>(p.q_sparse_dense + (size_t)row * (k / 2) + (size_t)group * 16) = qs;
+      } else {
+        *reinterpret_cast<uint2 *>(p.a_comp + (size_t)row * (k / 4) + (size_t)group * 8) = make_uint2(o.a_comp[0], o.a_comp[1]);
+      }
     }
-  }
-  // Metadata: rows up to ceil128(M), columns up to ceil256(K); dead lanes write zeros.
-  // One warp writes 4 rows x 16 B = 64 contiguous bytes.
-  if (!kDebug) {
-    // combine the 16-bit metadata of two neighbouring groups into one 32-bit store
-    uint32_t mine = o.meta & 0xFFFFu;
-    uint32_t other = __shfl_down_sync(0xffffffffu, mine, 1);
-    if ((lane & 1) == 0) {
-      uint8_t *dst = p.e + (size_t)blockIdx.x * aligned_m * 16 + (size_t)row * 16 + (size_t)(lane & 7) * 2;
-      *reinterpret_cast<uint32_t *>(dst) = mine | (other << 16);
+    // Metadata: rows up to ceil128(M), columns up to ceil256(K); dead lanes write zeros.
+    // One warp writes 4 rows x 16 B = 64 contiguous bytes.
+    if (!kDebug) {
+      // combine the 16-bit metadata of two neighbouring groups into one 32-bit store
+      uint32_t mine = o.meta & 0xFFFFu;
+      uint32_t other = __shfl_down_sync(0xffffffffu, mine, 1);
+      if ((lane & 1) == 0) {
+        uint8_t *dst = p.e + (size_t)k_tile * aligned_m * 16 + (size_t)row * 16 + (size_t)group_in_tile * 2;
+        *reinterpret_cast<uint32_t *>(dst) = mine | (other << 16);
+      }
     }
-  }
-  // Scale factors: 4 neighbouring groups share one 32-bit word of the sparse layout,
-  // 2 neighbouring groups (4 residual scales) one word of the dense layout.
-  {
-    uint32_t s = o.sf_sparse;
-    uint32_t s1 = __shfl_down_sync(0xffffffffu, s, 1);
-    uint32_t s2 = __shfl_down_sync(0xffffffffu, s, 2);
-    uint32_t s3 = __shfl_down_sync(0xffffffffu, s, 3);
-    uint32_t r2 = o.sf_res;
-    uint32_t r2n = __shfl_down_sync(0xffffffffu, r2, 1);
-    if (col_ok) {
-      if ((lane & 3) == 0)
-        *reinterpret_cast<uint32_t *>(p.sfa_sparse + sf_offset(row, group, groups32)) = s | (s1 << 8) | (s2 << 16) | (s3 << 24);
-      if ((lane & 1) == 0)
-        *reinterpret_cast<uint32_t *>(p.sf_res + sf_offset(row, 2 * group, k / 16)) = r2 | (r2n << 16);
+    // Scale factors: 4 neighbouring groups share one 32-bit word of the sparse layout,
+    // 2 neighbouring groups (4 residual scales) one word of the dense layout.
+    {
+      uint32_t sv = o.sf_sparse;
+      uint32_t s1 = __shfl_down_sync(0xffffffffu, sv, 1);
+      uint32_t s2 = __shfl_down_sync(0xffffffffu, sv, 2);
+      uint32_t s3 = __shfl_down_sync(0xffffffffu, sv, 3);
+      uint32_t r2 = o.sf_res;
+      uint32_t r2n = __shfl_down_sync(0xffffffffu, r2, 1);
+      if (col_ok) {
+        if ((lane & 3) == 0)
+          *reinterpret_cast<uint32_t *>(p.sfa_sparse + sf_offset(row, group, groups32)) = sv | (s1 << 8) | (s2 << 16) | (s3 << 24);
+        if ((lane & 1) == 0)
+          *reinterpret_cast<uint32_t *>(p.sf_res + sf_offset(row, 2 * group, k / 16)) = r2 | (r2n << 16);
+      }
     }
   }
 }
@@ -393,8 +494,18 @@ __global__ void __launch_bounds__(kPrepareThreads) prepare_kernel(const PrepareP
 
 size_t prepare_workspace_bytes(int m) { return 256 + (size_t)m * sizeof(float); }
 
+static int prepare_grid(const PrepareParams &p) {
+  static int sms[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148 * kPrepareCtasPerSm;
+  if (sms[dev] == 0 && cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms[dev] = 148;
+  const int tiles = ((p.k + kColsPerCta - 1) / kColsPerCta) * p.row_tiles;
+  const int full = sms[dev] * kPrepareCtasPerSm;
+  return tiles < full ? tiles : full;
+}
+
 static cudaError_t launch_prepare(int mode, bool debug, const PrepareParams &p, cudaStream_t stream) {
-  dim3 grid((p.k + kColsPerCta - 1) / kColsPerCta, p.row_tiles + kTailCtas);
+  dim3 grid(prepare_grid(p));
   dim3 block(kPrepareThreads);
   if (debug) {
     prepare_kernel<0, true><<<grid, block, 0, stream>>>(p);
@@ -433,21 +544,17 @@ cudaError_t run_scaled_prepare(const void *x, const void *gamma, float eps, int 
                                     : reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + 256);
   cudaError_t err = cudaMemsetAsync(amax_bits, 0, sizeof(unsigned int), stream);
   if (err != cudaSuccess) return err;
-  const int warps = 8;
-  dim3 grid((m + warps - 1) / warps), block(32 * warps);
   const bool rms = gamma != nullptr;
   if (rms) {
-    size_t smem = (size_t)warps * (k / 32) * sizeof(float);
-    if (smem > 48 * 1024) {
-      err = cudaFuncSetAttribute(row_stats_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (err != cudaSuccess) return err;
-    }
-    row_stats_kernel<true><<<grid, block, smem, stream>>>(static_cast<const __nv_bfloat16 *>(x),
-                                                         static_cast<const __nv_bfloat16 *>(gamma), eps, m, k,
-                                                         inv_rms, amax_bits);
+    const int groups = k / 32;
+    const int threads = (groups + 31) / 32 * 32;
+    rms_stats_kernel<<<m, threads, (size_t)groups * sizeof(float), stream>>>(
+        static_cast<const __nv_bfloat16 *>(x), static_cast<const __nv_bfloat16 *>(gamma), eps, k, inv_rms, amax_bits);
   } else {
-    row_stats_kernel<false><<<grid, block, 0, stream>>>(static_cast<const __nv_bfloat16 *>(x), nullptr, 0.0f, m, k,
-                                                        nullptr, amax_bits);
+    const size_t n16 = (size_t)m * k / 8;
+    size_t blocks = (n16 + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    abs_stats_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(x), n16, amax_bits);
   }
   err = cudaGetLastError();
   if (err != cudaSuccess) return err;

@@ -16,6 +16,7 @@ Extra ops that the reference does not have (all optional for a drop-in):
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 from typing import Optional, Tuple
 
@@ -36,7 +37,7 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def _stream(device: torch.device):
-    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    return torch.cuda.current_stream(device).cuda_stream
 
 
 def _error_flag(device: torch.device) -> torch.Tensor:
@@ -95,13 +96,12 @@ def fused_sparse_residual_quantize_x(X: torch.Tensor, N: int):
     """-> (A_comp, E, SFA_sparse, Q_res [M,K/2], SF_res)."""
     M, K = _check_x(X)
     _check(K % 128 == 0, f"fused_sparse_residual_quantize_x currently requires K to be a multiple of 128, got {K}")
-    sa, se, ssf, _, ssr = get_fused_sparse_residual_buffer_sizes(M, N, K)
     dev = X.device
-    A_comp, E, SFA, SF_res = _u8(sa, dev), _u8(se, dev), _u8(ssf, dev), _u8(ssr, dev)
-    Q_res = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
-    with torch.cuda.device(dev):
+    A_comp, E, SFA, Q_res, SF_res, _ = _prepare_buffers(M, K, dev)
+    with _on_device(dev):
         _lib.check(_lib.lib().sharq_fused_sparse_residual_quantize_x(
-            _ptr(X), M, N, K, _ptr(A_comp), _ptr(E), _ptr(SFA), _ptr(Q_res), _ptr(SF_res), _stream(dev)))
+            X.data_ptr(), M, N, K, A_comp.data_ptr(), E.data_ptr(), SFA.data_ptr(), Q_res.data_ptr(),
+            SF_res.data_ptr(), _stream(dev)))
     return A_comp, E, SFA, Q_res, SF_res
 
 
@@ -120,24 +120,53 @@ def fused_sparse_residual_quantize_x_debug(X: torch.Tensor, N: int):
     return Q_sparse, SFA, Q_res, SF_res
 
 
+def _round256(n: int) -> int:
+    return (n + 255) & ~255
+
+
+def _prepare_buffers(M: int, K: int, dev, extra: int = 0):
+    """One allocation for the five prepare outputs (+ `extra` trailing bytes), returned as
+    256-byte aligned views: (A_comp, E, SFA_sparse, Q_res [M,K/2], SF_res, tail)."""
+    k256 = (K + 255) // 256 * 256
+    sa = M * k256 // 4
+    se = ((M + 127) // 128 * 128) * k256 // 16
+    ssf = _sf_bytes(M, K)
+    sq = M * (K // 2)
+    o1 = _round256(sa)
+    o2 = o1 + _round256(se)
+    o3 = o2 + _round256(ssf)
+    o4 = o3 + _round256(sq)
+    o5 = o4 + _round256(ssf)
+    buf = torch.empty(o5 + extra, dtype=torch.uint8, device=dev)
+    return (buf[:sa], buf[o1:o1 + se], buf[o2:o2 + ssf], buf[o3:o3 + sq].view(M, K // 2), buf[o4:o4 + ssf],
+            buf[o5:o5 + extra])
+
+
+def _on_device(dev):
+    """Context that makes `dev` current; free when it already is."""
+    idx = dev.index
+    if idx is None or idx == torch.cuda.current_device():
+        return contextlib.nullcontext()
+    return torch.cuda.device(dev)
+
+
 def _scaled_prepare(X, gamma, eps, N, return_workspace):
     M, K = int(X.shape[0]), int(X.shape[1])
-    sa, se, ssf, _, ssr = get_fused_sparse_residual_buffer_sizes(M, N, K)
     dev = X.device
-    A_comp, E, SFA, SF_res = _u8(sa, dev), _u8(se, dev), _u8(ssf, dev), _u8(ssr, dev)
-    Q_res = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
-    scale = torch.empty((), dtype=torch.float32, device=dev)
-    ws_bytes = int(_lib.lib().sharq_prepare_workspace_bytes(M))
-    ws = _u8(ws_bytes, dev)
-    with torch.cuda.device(dev):
+    ws_bytes = 256 + 4 * M
+    A_comp, E, SFA, Q_res, SF_res, tail = _prepare_buffers(M, K, dev, extra=_round256(ws_bytes) + 256)
+    ws = tail[:ws_bytes]
+    scale = tail[_round256(ws_bytes):_round256(ws_bytes) + 4].view(torch.float32).reshape(())
+    L = _lib.lib()
+    with _on_device(dev):
         if gamma is not None:
-            _lib.check(_lib.lib().sharq_fused_rmsnorm_sparse_residual_quantize_x(
-                _ptr(X), _ptr(gamma), float(eps), M, N, K, _ptr(ws), ws_bytes, _ptr(A_comp), _ptr(E), _ptr(SFA),
-                _ptr(Q_res), _ptr(SF_res), _ptr(scale), _stream(dev)))
+            _lib.check(L.sharq_fused_rmsnorm_sparse_residual_quantize_x(
+                X.data_ptr(), gamma.data_ptr(), float(eps), M, N, K, ws.data_ptr(), ws_bytes, A_comp.data_ptr(),
+                E.data_ptr(), SFA.data_ptr(), Q_res.data_ptr(), SF_res.data_ptr(), scale.data_ptr(), _stream(dev)))
         else:
-            _lib.check(_lib.lib().sharq_scaled_sparse_residual_quantize_x(
-                _ptr(X), M, N, K, _ptr(ws), ws_bytes, _ptr(A_comp), _ptr(E), _ptr(SFA), _ptr(Q_res), _ptr(SF_res),
-                _ptr(scale), _stream(dev)))
+            _lib.check(L.sharq_scaled_sparse_residual_quantize_x(
+                X.data_ptr(), M, N, K, ws.data_ptr(), ws_bytes, A_comp.data_ptr(), E.data_ptr(), SFA.data_ptr(),
+                Q_res.data_ptr(), SF_res.data_ptr(), scale.data_ptr(), _stream(dev)))
     if return_workspace:
         return A_comp, E, SFA, Q_res, SF_res, scale, ws
     return A_comp, E, SFA, Q_res, SF_res, scale
@@ -271,7 +300,7 @@ def _dense_gemm(A, B, SFA, SFB, alpha, alpha_t, C_in, beta):
     M, N, K = int(A.shape[0]), int(B.shape[0]), int(A.shape[1]) * 2
     dev = A.device
     D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         _lib.check(_lib.lib().sharq_matmul(
             _ptr(A), _ptr(B), _ptr(SFA), _ptr(SFB), M, N, K, float(alpha),
             None if alpha_t is None else _scale_ptr(alpha_t, A, "scale"), _ptr(C_in), float(beta), _ptr(D),
@@ -328,7 +357,7 @@ def _sparse_gemm(name, A_comp, B, E, SFA, SFB, M, N, K, alpha, alpha_t, beta):
     _check(B.shape[1] == K // 2, f"B.size(1) mismatch: expected {K // 2}, got {B.shape[1]}")
     dev = A_comp.device
     D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         _lib.check(_lib.lib().sharq_sparse_matmul(
             _ptr(A_comp), _ptr(B), _ptr(E), _ptr(SFA), _ptr(SFB), M, N, K, float(alpha),
             None if alpha_t is None else _scale_ptr(alpha_t, A_comp, "alpha"), float(beta), _ptr(D),
@@ -359,7 +388,7 @@ def sharq_linear_gemm(A_comp, E, SFA_sparse, Q_res, SF_res, QW, SFW_sparse, SFW_
                "bias must be a contiguous CUDA bfloat16 tensor with N elements")
     D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
     alpha_t = alpha if isinstance(alpha, torch.Tensor) else None
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         _lib.check(_lib.lib().sharq_linear_gemm(
             _ptr(A_comp), _ptr(E), _ptr(SFA_sparse), _ptr(Q_res), _ptr(SF_res), _ptr(QW), _ptr(SFW_sparse),
             _ptr(SFW_dense), M, N, K, float(alpha_host) if alpha_t is not None else float(alpha) * float(alpha_host),
