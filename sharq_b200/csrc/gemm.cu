@@ -42,6 +42,14 @@ namespace {
 constexpr int kBM = 128;
 constexpr int kBK = 256;  // logical K per stage
 constexpr int kEpiWarps = 8;
+#ifdef SHARQ_GEMM_TIMING
+__device__ unsigned long long g_timing[8];
+#define TIMING_T0() long long t0_ = clock64()
+#define TIMING_ADD(slot) do { atomicAdd(&g_timing[slot], (unsigned long long)(clock64() - t0_)); t0_ = clock64(); } while (0)
+#else
+#define TIMING_T0() do {} while (0)
+#define TIMING_ADD(slot) do {} while (0)
+#endif
 constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 
 // Shared-memory stage and tensor-memory column layout.  In pair mode BN is the pair's tile
@@ -221,17 +229,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         for (int it = 0; it < k_stages; ++it, ++g) {
           const int s = (int)(g % S);
           const uint32_t ph = (g / S) & 1u;
+          TIMING_T0();
           if (!ptx::mbar_wait(empty_bar + s, ph ^ 1u, abort_flag)) {
             *abort_flag = 1;
             atomicExch(p.error_flag, 1);
             ok = false;
             break;
           }
+          TIMING_ADD(0);
           uint8_t *st = smem + s * L::kStageBytes;
           const int n_sp = SPARSE ? min(2, tiles_sp - 2 * it) : 0;
           const int n_d = DENSE ? min(4, tiles_d - 4 * it) : 0;
           uint32_t tx = L::kWBytes + L::kADenseBytes + L::kACompBytes + L::kEBytes;
           tx += (uint32_t)(n_sp * 512 * (1 + L::kBands) + n_d * 512 * (1 + L::kBands));
+#ifdef SHARQ_GEMM_NOLOAD
+          // debug experiment: after the first pass over the ring, re-arm the stage without copying
+          if (g >= (uint32_t)S) {
+            ptx::mbar_arrive(full_bar + s);
+            continue;
+          }
+#endif
           ptx::mbar_arrive_expect_tx(full_bar + s, tx);
           ptx::tma_load_2d(st + L::kOffW, &tm_w, it * 128, w_row, full_bar + s);
           if (DENSE) {
@@ -256,6 +273,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                                 p.sfb_sparse + ((size_t)(n_tile * L::kBands + b) * tiles_sp + 2 * (size_t)it) * 512,
                                 (uint32_t)n_sp * 512, full_bar + s);
           }
+          TIMING_ADD(1);
         }
       }
     }
@@ -286,8 +304,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         bool ok = true;
         for (int u = unit0; u < num_units && ok; u += unit_stride, ++tile_iter) {
           // the epilogue warps must have pulled the previous tile out of tensor memory
+          TIMING_T0();
           const bool drained = PAIR ? ptx::mbar_wait_cluster(acc_empty_bar, (tile_iter & 1u) ^ 1u, abort_flag)
                                     : ptx::mbar_wait(acc_empty_bar, (tile_iter & 1u) ^ 1u, abort_flag);
+          TIMING_ADD(5);
           if (!drained) {
             *abort_flag = 1;
             atomicExch(p.error_flag, 5);
@@ -298,8 +318,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           for (int it = 0; it < k_stages; ++it, ++g) {
             const int s = (int)(g % S);
             const uint32_t ph = (g / S) & 1u;
+            TIMING_T0();
             bool got = ptx::mbar_wait(full_bar + s, ph, abort_flag);
+            TIMING_ADD(2);
             if (PAIR && got) got = ptx::mbar_wait_cluster(peer_bar + s, ph, abort_flag);
+            TIMING_ADD(3);
             if (!got) {
               *abort_flag = 1;
               atomicExch(p.error_flag, 2);
@@ -370,6 +393,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               ptx::tc_commit_multicast2(empty_bar + s, 3);
             else
               ptx::tc_commit<1>(empty_bar + s);
+            TIMING_ADD(4);
           }
           if (ok) {
             if (PAIR)
@@ -551,6 +575,17 @@ cudaError_t launch(const GemmArgs &a, cudaStream_t stream) {
 }
 
 }  // namespace
+
+#ifdef SHARQ_GEMM_TIMING
+extern "C" int sharq_debug_read_timing(unsigned long long *out, int reset) {
+  if (cudaMemcpyFromSymbol(out, g_timing, sizeof(g_timing)) != cudaSuccess) return 1;
+  if (reset) {
+    unsigned long long z[8] = {};
+    if (cudaMemcpyToSymbol(g_timing, z, sizeof(z)) != cudaSuccess) return 1;
+  }
+  return 0;
+}
+#endif
 
 cudaError_t run_gemm(const GemmArgs &a, cudaStream_t stream) {
   const bool sparse = a.a_comp != nullptr;
