@@ -296,7 +296,40 @@ def run_ours(args):
         "gemm_time_share": round(gemm_share, 3),
     }
 
+    # ---- whole-model prefill (config 2: Llama-3-8B shape, batch 1 x seqlen M): the same linears
+    # chained through RoPE attention, SwiGLU and residuals; reported beside the headline metric
+    prefill = None
+    if args.prefill_steps > 0:
+        from sharq_b200.decoder import DecoderConfig, SharqDecoder
+
+        layers.clear()
+        graph_keep = graph  # the captured step stays alive until teardown
+        torch.cuda.empty_cache()
+        model = SharqDecoder(DecoderConfig.llama3_8b(layers=layers_n), dev, world=world, rank=rank, seed=7)
+        ids = torch.randint(0, model.cfg.vocab, (1, m), generator=torch.Generator().manual_seed(0)).to(dev)
+        for _ in range(2):
+            logits = model.prefill(ids)
+        barrier()
+        ops.check_device_errors()
+        pg = None
+        if not args.no_graph:
+            pg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(pg):
+                logits = model.prefill(ids)
+            pg.replay()
+            barrier()
+        ms_prefill = timed((lambda: pg.replay()) if pg is not None else (lambda: model.prefill(ids)),
+                           args.prefill_steps) / args.prefill_steps
+        assert torch.isfinite(logits).all()
+        prefill = {"model": f"llama3-8b shape, {layers_n} layers, random init, tp{world}", "batch": 1, "seq_len": m,
+                   "ms": round(ms_prefill, 3), "tokens_per_s": round(m / (ms_prefill * 1e-3), 1),
+                   "launch": "eager" if pg is None else "one CUDA graph"}
+        if pg is not None:
+            pg.reset()
+        del model
+
     result = {
+        "prefill": prefill,
         "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4", "data": "synthetic",
@@ -440,6 +473,7 @@ def main():
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--ref-tokens", type=int, default=128)
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--prefill-steps", type=int, default=3, help="0 skips the whole-model prefill measurement")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph replay")
     args = ap.parse_args()
     if args.impl == "reference":

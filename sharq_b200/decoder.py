@@ -1,0 +1,186 @@
+"""Minimal decoder stacks (Llama / Qwen2 shaped) built on the SharQ linears, for prefill.
+
+The reference wraps HuggingFace decoder layers (model/qLlamaLayer.py:50-257,
+model/qQwenLayer.py) written against transformers 4.44; those wrappers read attributes
+that newer transformers releases no longer have, so this module carries its own small
+decoder with the same call pattern on the quantized path:
+
+* one prepared activation is shared by q, k and v (here one merged qkv GEMM) and by
+  gate and up (one merged gate_up GEMM)            - model/qLlamaLayer.py:93-106,173-183
+* the input and post-attention RMSNorms are fused into the prepare of the following
+  linears; the decoder layer never runs them separately - model/qLlamaLayer.py:219-221
+* o_proj and down_proj take the plain (non-RMSNorm) prepare
+* attention itself is stock `scaled_dot_product_attention` with RoPE and grouped KV heads;
+  it is not part of the accelerated path.
+
+Tensor parallelism (`world` > 1): attention heads and the FFN width are sharded; qkv and
+gate_up are column-parallel, o_proj and down_proj row-parallel with an all-reduce.
+Weights are random (N(0, 0.02)): there are no checkpoints in this environment.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from .tp import RowParallelSharqLinear, shard_bounds
+
+
+@dataclass
+class DecoderConfig:
+    hidden: int = 4096
+    layers: int = 32
+    heads: int = 32
+    kv_heads: int = 8
+    head_dim: int = 128
+    ffn: int = 14336
+    vocab: int = 128256
+    rope_theta: float = 5e5
+    eps: float = 1e-6
+    qkv_bias: bool = False
+
+    @staticmethod
+    def llama3_8b(**kw):
+        return DecoderConfig(**kw)
+
+    @staticmethod
+    def qwen25_7b(**kw):
+        return DecoderConfig(hidden=3584, layers=28, heads=28, kv_heads=4, head_dim=128, ffn=18944, vocab=152064,
+                             rope_theta=1e6, qkv_bias=True, **kw)
+
+
+def rope_tables(seq: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
+    ang = torch.outer(torch.arange(seq, device=device, dtype=torch.float32), inv)
+    emb = torch.cat((ang, ang), dim=-1)
+    return emb.cos().to(torch.bfloat16), emb.sin().to(torch.bfloat16)
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x: [B, H, S, D]; rotate-half convention."""
+    half = x.shape[-1] // 2
+    rot = torch.cat((-x[..., half:], x[..., :half]), dim=-1)
+    return x * cos + rot * sin
+
+
+class SharqDecoderLayer(torch.nn.Module):
+    def __init__(self, cfg: DecoderConfig, gen: torch.Generator, device, world: int = 1, rank: int = 0,
+                 keep_reference: bool = False):
+        super().__init__()
+        self.cfg, self.world, self.rank = cfg, world, rank
+        self.ref = {} if keep_reference else None  # unquantised bf16 weights, for accuracy checks only
+        h, d = cfg.hidden, cfg.head_dim
+        if cfg.heads % world or cfg.kv_heads % world:
+            raise ValueError(f"{cfg.heads} query / {cfg.kv_heads} KV heads do not split over {world} ranks; pad first")
+        self.local_heads, self.local_kv = cfg.heads // world, cfg.kv_heads // world
+
+        def rnd(n, k):
+            return (0.02 * torch.randn(n, k, generator=gen, device=device)).to(torch.bfloat16)
+
+        # every rank draws the same full weights (same generator state) and keeps its shard
+        wq, wk, wv = rnd(cfg.heads * d, h), rnd(cfg.kv_heads * d, h), rnd(cfg.kv_heads * d, h)
+        qb, qe = shard_bounds(cfg.heads * d, world, rank, 128)
+        kb, ke = shard_bounds(cfg.kv_heads * d, world, rank, 128)
+        bias = None
+        if cfg.qkv_bias:
+            bq, bk, bv = (0.02 * torch.randn(n, generator=gen, device=device) for n in
+                          (cfg.heads * d, cfg.kv_heads * d, cfg.kv_heads * d))
+            bias = torch.cat((bq[qb:qe], bk[kb:ke], bv[kb:ke])).to(torch.bfloat16)
+        self.qkv = _local_column(torch.cat((wq[qb:qe], wk[kb:ke], wv[kb:ke])), torch.cat((wq, wk, wv)), bias)
+        wo = rnd(h, cfg.heads * d)
+        self.o_proj = RowParallelSharqLinear(wo)
+        wg, wu = rnd(cfg.ffn, h), rnd(cfg.ffn, h)
+        fb, fe = shard_bounds(cfg.ffn, world, rank, 128)
+        self.gate_up = _local_column(torch.cat((wg[fb:fe], wu[fb:fe])), torch.cat((wg, wu)), None)
+        wd = rnd(h, cfg.ffn)
+        self.down = RowParallelSharqLinear(wd)
+        if keep_reference:
+            self.ref = dict(qkv=torch.cat((wq, wk, wv)), qkv_bias=bias, o=wo, gate=wg, up=wu, down=wd)
+        del wq, wk, wv, wo, wg, wu, wd
+        self.input_norm = (1 + 0.1 * torch.randn(h, generator=gen, device=device)).to(torch.bfloat16)
+        self.post_norm = (1 + 0.1 * torch.randn(h, generator=gen, device=device)).to(torch.bfloat16)
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        """x: [B, S, hidden] bf16 -> same shape."""
+        cfg = self.cfg
+        b, s, h = x.shape
+        x2 = x.reshape(b * s, h)
+        prep = self.qkv.prepare_input_rmsnorm(x2, self.input_norm, cfg.eps)
+        qkv = self.qkv.apply_prepared(prep)
+        nq, nk = self.local_heads * cfg.head_dim, self.local_kv * cfg.head_dim
+        q = qkv[:, :nq].view(b, s, self.local_heads, cfg.head_dim).transpose(1, 2)
+        k = qkv[:, nq:nq + nk].view(b, s, self.local_kv, cfg.head_dim).transpose(1, 2)
+        v = qkv[:, nq + nk:].view(b, s, self.local_kv, cfg.head_dim).transpose(1, 2)
+        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+        attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+        attn2 = attn.transpose(1, 2).reshape(b * s, nq)
+        x2 = x2 + self.o_proj(attn2)
+        prep = self.gate_up.prepare_input_rmsnorm(x2, self.post_norm, cfg.eps)
+        gu = self.gate_up.apply_prepared(prep)
+        f = gu.shape[1] // 2
+        x2 = x2 + self.down(F.silu(gu[:, :f]) * gu[:, f:])
+        return x2.view(b, s, h)
+
+
+    @torch.no_grad()
+    def forward_reference(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        """The same layer with the unquantised bf16 weights (single rank, keep_reference=True)."""
+        cfg, r = self.cfg, self.ref
+        b, s, h = x.shape
+
+        def norm(t, w):
+            tf = t.float()
+            return (tf * torch.rsqrt(tf.pow(2).mean(-1, keepdim=True) + cfg.eps) * w.float()).to(torch.bfloat16)
+
+        x2 = x.reshape(b * s, h)
+        qkv = F.linear(norm(x2, self.input_norm), r["qkv"], r["qkv_bias"])
+        nq, nk = cfg.heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim
+        q = qkv[:, :nq].view(b, s, cfg.heads, cfg.head_dim).transpose(1, 2)
+        k = qkv[:, nq:nq + nk].view(b, s, cfg.kv_heads, cfg.head_dim).transpose(1, 2)
+        v = qkv[:, nq + nk:].view(b, s, cfg.kv_heads, cfg.head_dim).transpose(1, 2)
+        attn = F.scaled_dot_product_attention(apply_rope(q, cos, sin), apply_rope(k, cos, sin), v, is_causal=True,
+                                              enable_gqa=True)
+        x2 = x2 + F.linear(attn.transpose(1, 2).reshape(b * s, nq), r["o"])
+        y = norm(x2, self.post_norm)
+        x2 = x2 + F.linear(F.silu(F.linear(y, r["gate"])) * F.linear(y, r["up"]), r["down"])
+        return x2.view(b, s, h)
+
+
+def _local_column(w_local: torch.Tensor, w_full: torch.Tensor, bias):
+    """Column-parallel linear from an already gathered local slice; the weight tensor scale is
+    taken over the FULL weight so that shards agree with the unsharded layer."""
+    from . import ops
+    from .qlinear import QLinearLayer
+
+    scale = torch.clamp(w_full.abs().max().float() / (448.0 * 6.0), min=1e-9)
+    q, sfs, sfd = ops.quantize_w32_shared((w_local / scale).to(torch.bfloat16).contiguous())
+    return QLinearLayer.from_quantized(w_local.shape[1], w_local.shape[0], q, sfs, sfd, scale, bias=bias)
+
+
+class SharqDecoder(torch.nn.Module):
+    """Embedding -> N decoder layers -> final norm -> (bf16) lm_head on the last token."""
+
+    def __init__(self, cfg: DecoderConfig, device, world: int = 1, rank: int = 0, seed: int = 0,
+                 keep_reference: bool = False):
+        super().__init__()
+        self.cfg = cfg
+        gen = torch.Generator(device=device).manual_seed(seed)
+        self.embed = (0.02 * torch.randn(cfg.vocab, cfg.hidden, generator=gen, device=device)).to(torch.bfloat16)
+        self.layers = torch.nn.ModuleList([SharqDecoderLayer(cfg, gen, device, world, rank, keep_reference) for _ in range(cfg.layers)])
+        self.final_norm = (1 + 0.1 * torch.randn(cfg.hidden, generator=gen, device=device)).to(torch.bfloat16)
+        self.lm_head = (0.02 * torch.randn(cfg.vocab, cfg.hidden, generator=gen, device=device)).to(torch.bfloat16)
+
+    @torch.no_grad()
+    def prefill(self, token_ids: torch.Tensor, reference: bool = False) -> torch.Tensor:
+        """token_ids [B, S] -> logits of the last position [B, vocab] (float32).
+        reference=True runs the unquantised bf16 layers (needs keep_reference=True)."""
+        b, s = token_ids.shape
+        x = self.embed[token_ids]
+        cos, sin = rope_tables(s, self.cfg.head_dim, self.cfg.rope_theta, x.device)
+        for layer in self.layers:
+            x = layer.forward_reference(x, cos, sin) if reference else layer(x, cos, sin)
+        last = x[:, -1, :].float()
+        last = last * torch.rsqrt(last.pow(2).mean(-1, keepdim=True) + self.cfg.eps) * self.final_norm.float()
+        return (last.to(torch.bfloat16) @ self.lm_head.T).float()
