@@ -327,6 +327,21 @@ def run_ours(args):
         if pg is not None:
             pg.reset()
         del model
+        if args.compare and world == 1:
+            # the same stack with this project's dense-NVFP4 path and with plain bf16 linears
+            for mode in ("NVFP4", "BF16"):
+                torch.cuda.empty_cache()
+                other = SharqDecoder(DecoderConfig.llama3_8b(layers=layers_n), dev, seed=7, mode=mode)
+                for _ in range(2):
+                    other.prefill(ids)
+                og = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(og):
+                    other.prefill(ids)
+                og.replay()
+                ms_o = timed(lambda: og.replay(), args.prefill_steps) / args.prefill_steps
+                prefill[f"{mode.lower()}_tokens_per_s"] = round(m / (ms_o * 1e-3), 1)
+                og.reset()
+                del other
 
     result = {
         "prefill": prefill,
@@ -474,6 +489,7 @@ def main():
     ap.add_argument("--ref-tokens", type=int, default=128)
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--prefill-steps", type=int, default=3, help="0 skips the whole-model prefill measurement")
+    ap.add_argument("--compare", action="store_true", help="also time the prefill with dense NVFP4 and bf16 linears (1 GPU)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph replay")
     args = ap.parse_args()
     if args.impl == "reference":

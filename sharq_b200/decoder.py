@@ -66,10 +66,16 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
 
 class SharqDecoderLayer(torch.nn.Module):
     def __init__(self, cfg: DecoderConfig, gen: torch.Generator, device, world: int = 1, rank: int = 0,
-                 keep_reference: bool = False):
+                 keep_reference: bool = False, mode: str = "SHARQ"):
         super().__init__()
+        if mode not in ("SHARQ", "NVFP4", "BF16"):
+            raise ValueError(f"unknown mode {mode}")
+        if mode != "SHARQ" and world != 1:
+            raise ValueError("the NVFP4 and BF16 comparison modes are single-GPU only")
+        self.mode = mode
+        keep_reference = keep_reference or mode != "SHARQ"
         self.cfg, self.world, self.rank = cfg, world, rank
-        self.ref = {} if keep_reference else None  # unquantised bf16 weights, for accuracy checks only
+        self.ref = {} if keep_reference else None  # unquantised bf16 weights (accuracy checks, baselines)
         h, d = cfg.hidden, cfg.head_dim
         if cfg.heads % world or cfg.kv_heads % world:
             raise ValueError(f"{cfg.heads} query / {cfg.kv_heads} KV heads do not split over {world} ranks; pad first")
@@ -98,12 +104,34 @@ class SharqDecoderLayer(torch.nn.Module):
         if keep_reference:
             self.ref = dict(qkv=torch.cat((wq, wk, wv)), qkv_bias=bias, o=wo, gate=wg, up=wu, down=wd)
         del wq, wk, wv, wo, wg, wu, wd
+        if mode == "NVFP4":
+            # dense NVFP4 baseline: unfused RMSNorm, dense activation quantisation, dense GEMM
+            from .qlinear import QLinearLayer
+
+            def dense(w, b=None):
+                lin = torch.nn.Linear(w.shape[1], w.shape[0], bias=b is not None, device=device, dtype=torch.bfloat16)
+                lin.weight.data.copy_(w)
+                if b is not None:
+                    lin.bias.data.copy_(b)
+                return QLinearLayer(lin, quant_type="NVFP4", device=device)
+
+            r = self.ref
+            self.nv = dict(qkv=dense(r["qkv"], r["qkv_bias"]), o=dense(r["o"]),
+                           gate_up=dense(torch.cat((r["gate"], r["up"]))), down=dense(r["down"]))
+            self.ref = None
+            self.qkv = self.o_proj = self.gate_up = self.down = None
+        elif mode == "BF16":
+            self.qkv = self.o_proj = self.gate_up = self.down = None
         self.input_norm = (1 + 0.1 * torch.randn(h, generator=gen, device=device)).to(torch.bfloat16)
         self.post_norm = (1 + 0.1 * torch.randn(h, generator=gen, device=device)).to(torch.bfloat16)
 
     @torch.no_grad()
     def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
         """x: [B, S, hidden] bf16 -> same shape."""
+        if self.mode == "BF16":
+            return self.forward_reference(x, cos, sin)
+        if self.mode == "NVFP4":
+            return self._forward_nvfp4(x, cos, sin)
         cfg = self.cfg
         b, s, h = x.shape
         x2 = x.reshape(b * s, h)
@@ -123,6 +151,24 @@ class SharqDecoderLayer(torch.nn.Module):
         x2 = x2 + self.down(F.silu(gu[:, :f]) * gu[:, f:])
         return x2.view(b, s, h)
 
+
+    @torch.no_grad()
+    def _forward_nvfp4(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        cfg, nv = self.cfg, self.nv
+        b, s, h = x.shape
+        x2 = x.reshape(b * s, h)
+        qkv = nv["qkv"].apply_prepared(nv["qkv"].prepare_input_rmsnorm(x2, self.input_norm, cfg.eps))
+        nq, nk = cfg.heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim
+        q = qkv[:, :nq].view(b, s, cfg.heads, cfg.head_dim).transpose(1, 2)
+        k = qkv[:, nq:nq + nk].view(b, s, cfg.kv_heads, cfg.head_dim).transpose(1, 2)
+        v = qkv[:, nq + nk:].view(b, s, cfg.kv_heads, cfg.head_dim).transpose(1, 2)
+        attn = F.scaled_dot_product_attention(apply_rope(q, cos, sin), apply_rope(k, cos, sin), v, is_causal=True,
+                                              enable_gqa=True)
+        x2 = x2 + nv["o"](attn.transpose(1, 2).reshape(b * s, nq))
+        gu = nv["gate_up"].apply_prepared(nv["gate_up"].prepare_input_rmsnorm(x2, self.post_norm, cfg.eps))
+        f = gu.shape[1] // 2
+        x2 = x2 + nv["down"](F.silu(gu[:, :f]) * gu[:, f:])
+        return x2.view(b, s, h)
 
     @torch.no_grad()
     def forward_reference(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
@@ -163,12 +209,12 @@ class SharqDecoder(torch.nn.Module):
     """Embedding -> N decoder layers -> final norm -> (bf16) lm_head on the last token."""
 
     def __init__(self, cfg: DecoderConfig, device, world: int = 1, rank: int = 0, seed: int = 0,
-                 keep_reference: bool = False):
+                 keep_reference: bool = False, mode: str = "SHARQ"):
         super().__init__()
         self.cfg = cfg
         gen = torch.Generator(device=device).manual_seed(seed)
         self.embed = (0.02 * torch.randn(cfg.vocab, cfg.hidden, generator=gen, device=device)).to(torch.bfloat16)
-        self.layers = torch.nn.ModuleList([SharqDecoderLayer(cfg, gen, device, world, rank, keep_reference) for _ in range(cfg.layers)])
+        self.layers = torch.nn.ModuleList([SharqDecoderLayer(cfg, gen, device, world, rank, keep_reference, mode) for _ in range(cfg.layers)])
         self.final_norm = (1 + 0.1 * torch.randn(cfg.hidden, generator=gen, device=device)).to(torch.bfloat16)
         self.lm_head = (0.02 * torch.randn(cfg.vocab, cfg.hidden, generator=gen, device=device)).to(torch.bfloat16)
 
