@@ -280,7 +280,10 @@ def run_ours(args):
     achieved = alg_flops / (gemm_ms * 1e-3) / 1e12
     roofline = {"bound": "tensor", "kernel": "gemm_kernel<256,sparse+dense> (gate_up)", "achieved": round(achieved, 1),
                 "peak": round(p_dense_fp4, 1), "unit": "TFLOP/s", "frac": round(achieved / p_dense_fp4, 4),
-                "traffic": None,
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this shape on
+                # one GPU (ncu capture summarised in profiles/gemm_kernel_fused_pair.md); algorithmic bytes
+                # are 195 MB (78 MB of operands, 117 MB of output, part of which is still in L2 at kernel end)
+                "traffic": 149.8e6 if world == 1 and m == 2048 else None,
                 "peak_source": f"4 x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS (dense FP4 = 4 x bf16 rate)",
                 "flops_convention": "3*M*N*K dense-FP4-equivalent (2MNK dense pass + 2MNK sparse pass at 2x rate)",
                 "avg_launch_ms": round(gemm_ms, 4)}

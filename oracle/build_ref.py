@@ -1,0 +1,71 @@
+"""Builds oracle/_ref/libsharq_ref.so: the REFERENCE's own CUDA kernels for the hot path,
+compiled in place from the reference checkout (no source is copied) with a short nvcc
+recipe, plus the extern "C" shims of oracle/ref_wrap.cu.  TEST INFRASTRUCTURE ONLY.
+
+    python oracle/build_ref.py [/path/to/reference] [--gemm]
+
+The reference needs NVIDIA CUTLASS, an un-vendored and unpinned submodule of its repository;
+the CUTLASS 4.5.0 headers shipped inside the flashinfer wheel are used instead (the version
+the reference's authors built with is unknown).  Its own build system (cmake + torch) is
+not run.  Without --gemm only the quantisation kernels are built (about 2 minutes); with
+--gemm also its two CUTLASS GEMM wrappers (several more minutes).  The library is
+optional: tests that use it skip when it is absent.
+"""
+from __future__ import annotations
+
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+OUT = HERE / "_ref"
+QUANT_SOURCES = ["fused_sparse_prepare.cu", "fused_rmsnorm_sparse_prepare.cu", "shared_weight_nvfp4.cu", "reorder.cu"]
+GEMM_SOURCES = ["nvfp4.cu", "sparse_nvfp4.cu"]
+
+
+def cutlass_root() -> Path:
+    import flashinfer  # only to locate the vendored headers
+
+    root = Path(flashinfer.__file__).parent / "data" / "cutlass"
+    if not (root / "include" / "cutlass" / "cutlass.h").exists():
+        raise SystemExit("CUTLASS headers not found; oracle/_ref not built")
+    return root
+
+
+def build(ref: Path = Path("/root/reference"), with_gemm: bool = False) -> None:
+    if not (ref / "kernels" / "src").exists():
+        raise SystemExit(f"no reference checkout at {ref}; oracle/_ref not built")
+    cut = cutlass_root()
+    OUT.mkdir(exist_ok=True)
+    obj = OUT / "obj"
+    obj.mkdir(exist_ok=True)
+    stub = OUT / "stub"
+    stub.mkdir(exist_ok=True)
+    # the reference includes CUTLASS's examples/common/helper.h but uses nothing from it
+    (stub / "helper.h").write_text("#pragma once\n")
+    flags = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "--expt-relaxed-constexpr", "-w",
+             "-Xcompiler", "-fPIC", "-Xcompiler", "-fpermissive", "-DSHARQ_TARGET_SM100A",
+             f"-I{ref / 'kernels' / 'include'}", f"-I{cut / 'include'}", f"-I{cut / 'tools' / 'util' / 'include'}",
+             f"-I{stub}"]
+    sources = [ref / "kernels" / "src" / s for s in QUANT_SOURCES + (GEMM_SOURCES if with_gemm else [])]
+    sources.append(HERE / "ref_wrap.cu")
+    defs = ["-DSHARQ_REF_WITH_GEMM"] if with_gemm else []
+
+    def compile_one(src: Path) -> Path:
+        o = obj / (src.name + ".o")
+        if o.exists() and o.stat().st_mtime > src.stat().st_mtime:
+            return o
+        subprocess.run(["nvcc", *flags, *defs, "-c", str(src), "-o", str(o)], check=True)
+        return o
+
+    with ThreadPoolExecutor(max_workers=4) as pool:
+        objs = list(pool.map(compile_one, sources))
+    name = "libsharq_ref_gemm.so" if with_gemm else "libsharq_ref.so"
+    subprocess.run(["nvcc", "-shared", "-o", str(OUT / name), *map(str, objs)], check=True)
+    print(OUT / name)
+
+
+if __name__ == "__main__":
+    _args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    build(Path(_args[0]) if _args else Path("/root/reference"), "--gemm" in sys.argv)

@@ -1,0 +1,125 @@
+"""Bit-exact parity with the REFERENCE's own CUDA kernels.
+
+oracle/_ref/libsharq_ref.so holds the reference's quantisation kernels compiled in place
+from its sources (recipe: oracle/build_ref.py).  These tests run them and this project's
+kernels on the same device buffers and require identical bytes.  They skip when the
+library has not been built (it needs the reference checkout and CUTLASS headers)."""
+import ctypes
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+REF_SO = Path(__file__).resolve().parent.parent / "oracle" / "_ref" / "libsharq_ref.so"
+
+
+@pytest.fixture(scope="module")
+def ref():
+    if not REF_SO.exists():
+        pytest.skip("oracle/_ref/libsharq_ref.so not built")
+    return ctypes.CDLL(str(REF_SO))
+
+
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _zeros(n):
+    return torch.zeros(int(n), dtype=torch.uint8, device="cuda")  # the reference op zero-fills its outputs
+
+
+@pytest.mark.parametrize("m,k,case", [(512, 4096, "config0"), (130, 384, "config0"), (64, 1024, "outlier"),
+                                      (33, 256, "ties"), (2048, 4096, "config0")])
+def test_prepare_equals_reference_kernel(ref, m, k, case):
+    from sharq_b200 import ops
+
+    n = 256
+    if case == "config0":
+        x = H.config0_x(m, k, m)
+        x = (x.float() / (x.float().abs().max() / 2688)).to(torch.bfloat16)
+    elif case == "outlier":
+        x = H.outlier_rich_x(m, k, 1)
+    else:
+        x = H.tie_x(m, k, 2)
+    xd = x.cuda()
+    sizes = ops.get_fused_sparse_residual_buffer_sizes(m, n, k)
+    theirs = [_zeros(s) for s in sizes]
+    rc = ref.ref_fused_sparse_residual_x(_p(xd), m, n, k, _p(theirs[0]), _p(theirs[1]), None, _p(theirs[2]), _p(theirs[3]),
+                                         _p(theirs[4]))
+    torch.cuda.synchronize()
+    assert rc == 0
+    mine = ops.fused_sparse_residual_quantize_x(xd, n)
+    for name, a, b in zip(("a_comp", "e", "sfa_sparse", "q_res", "sf_res"), mine, theirs):
+        assert torch.equal(a.reshape(-1), b), name
+
+
+@pytest.mark.parametrize("m,k", [(512, 4096), (130, 512), (2048, 4096), (256, 14336)])
+def test_rmsnorm_prepare_equals_reference_kernels(ref, m, k):
+    """The reference's three steps (row stats kernel, ATen scale glue, fused kernel) against
+    this project's RMSNorm-fused prepare: inv_rms, scale and every output byte."""
+    from sharq_b200 import ops
+
+    n = 128
+    x = H.config0_x(m, k, 3 * m + k).cuda()
+    gamma = H.config0_gamma(k, m).cuda()
+    eps = 1e-6
+    inv = torch.zeros(m, dtype=torch.float32, device="cuda")
+    row_amax = torch.zeros(m, dtype=torch.float32, device="cuda")
+    assert ref.ref_rmsnorm_row_stats(_p(x), _p(gamma), ctypes.c_float(eps), m, k, _p(inv), _p(row_amax)) == 0
+    scale = torch.clamp(torch.amax(row_amax) / (448.0 * 6.0), 1.0e-9)  # kernels/src/bindings.cpp:337
+    sizes = ops.get_fused_sparse_residual_buffer_sizes(m, n, k)
+    theirs = [_zeros(s) for s in sizes]
+    assert ref.ref_rmsnorm_sparse_residual_x(_p(x), _p(gamma), _p(inv), _p(scale), m, n, k, _p(theirs[0]), _p(theirs[1]),
+                                             _p(theirs[2]), _p(theirs[3]), _p(theirs[4])) == 0
+    torch.cuda.synchronize()
+    out = ops.fused_rmsnorm_sparse_residual_quantize_x(x, gamma, eps, n, return_workspace=True)
+    ws = out[6]
+    my_inv = ws[256:256 + 4 * m].view(torch.float32)
+    assert torch.equal(my_inv, inv), "inv_rms differs from the reference's row-stats kernel"
+    assert torch.equal(out[5].reshape(()), scale.reshape(())), "tensor scale differs"
+    for name, a, b in zip(("a_comp", "e", "sfa_sparse", "q_res", "sf_res"), out[:5], theirs):
+        assert torch.equal(a.reshape(-1), b), name
+
+
+@pytest.mark.parametrize("n,k", [(256, 4096), (130, 512), (4096, 14336)])
+def test_weight_quant_equals_reference_kernel(ref, n, k):
+    from sharq_b200 import ops
+
+    w = H.config0_w(n, k, n)
+    w = (w.float() / (w.float().abs().max() / 2688)).to(torch.bfloat16).cuda()
+    sf = (n // 128 + 1) * 128 * k // 16
+    q = torch.zeros((n, k // 2), dtype=torch.uint8, device="cuda")
+    sfs, sfd = _zeros(sf), _zeros(sf)
+    assert ref.ref_quantize_w32_shared(_p(w), n, k, _p(q), _p(sfs), _p(sfd)) == 0
+    torch.cuda.synchronize()
+    mq, msfs, msfd = ops.quantize_w32_shared(w)
+    assert torch.equal(mq, q) and torch.equal(msfs, sfs) and torch.equal(msfd, sfd)
+
+
+@pytest.mark.parametrize("m,k", [(64, 4096), (130, 14336), (300, 2048)])
+def test_dense_quant_equals_reference_kernel(ref, m, k):
+    from sharq_b200 import ops
+
+    x = H.config0_x(m, k, k)
+    x = (x.float() / (x.float().abs().max() / 2688)).to(torch.bfloat16).cuda()
+    idx = torch.arange(k, dtype=torch.int16, device="cuda")
+    sf = (m // 128 + 1) * 128 * k // 16
+    q = torch.zeros((m, k // 2), dtype=torch.uint8, device="cuda")
+    s_ref = _zeros(sf)
+    assert ref.ref_quantize_x_dense(_p(x), m, k, _p(idx), _p(q), _p(s_ref)) == 0
+    torch.cuda.synchronize()
+    mq, ms = ops.quantize_x_nvfp4(x)
+    assert torch.equal(mq, q)
+    used = torch.from_numpy(H_sf_used(m, k)).cuda()
+    assert torch.equal(ms[used], s_ref[used])  # the reference leaves the other bytes undefined
+
+
+def H_sf_used(rows, k):
+    from oracle import sharq_oracle as O
+
+    return O.sf_offsets(rows, k // 16).reshape(-1)
