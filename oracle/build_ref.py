@@ -53,7 +53,7 @@ def build(ref: Path = Path("/root/reference"), with_gemm: bool = False) -> None:
     defs = ["-DSHARQ_REF_WITH_GEMM"] if with_gemm else []
 
     def compile_one(src: Path) -> Path:
-        o = obj / (src.name + ".o")
+        o = obj / (src.name + (".gemm.o" if (with_gemm and src.name == "ref_wrap.cu") else ".o"))
         if o.exists() and o.stat().st_mtime > src.stat().st_mtime:
             return o
         subprocess.run(["nvcc", *flags, *defs, "-c", str(src), "-o", str(o)], check=True)

@@ -123,3 +123,68 @@ def H_sf_used(rows, k):
     from oracle import sharq_oracle as O
 
     return O.sf_offsets(rows, k // 16).reshape(-1)
+
+
+def _time_us(fn, iters=30):
+    for _ in range(5):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e3
+
+
+@pytest.mark.skipif(__import__("os").environ.get("SHARQ_REF_PREPARE_TIMING") != "1",
+                    reason="set SHARQ_REF_PREPARE_TIMING=1 to time")
+def test_time_prepare_against_reference_kernels(ref):
+    """Kernel time only, both sides through their C entry points on preallocated buffers.
+    The reference side leaves out its ATen glue (amax, divide, clamp: four more launches)
+    and the zero-fill of its outputs, so it is a lower bound of the reference op."""
+    from sharq_b200 import _lib, ops
+    from tests.gpu_util import call, dptr, stream_ptr
+
+    m, n, eps = 2048, 4096, 1e-6
+    with torch.cuda.stream(torch.cuda.default_stream()):
+        for k in (4096, 14336):
+            x = H.config0_x(m, k, 5).cuda()
+            gamma = H.config0_gamma(k, 1).cuda()
+            sizes = ops.get_fused_sparse_residual_buffer_sizes(m, n, k)
+            out = [_zeros(s) for s in sizes]
+            inv = torch.zeros(m, dtype=torch.float32, device="cuda")
+            row_amax = torch.zeros(m, dtype=torch.float32, device="cuda")
+            scale = torch.ones(1, dtype=torch.float32, device="cuda")
+            ws = torch.zeros(int(_lib.lib().sharq_prepare_workspace_bytes(m)), dtype=torch.uint8, device="cuda")
+
+            def ref_rms():
+                ref.ref_rmsnorm_row_stats(_p(x), _p(gamma), ctypes.c_float(eps), m, k, _p(inv), _p(row_amax))
+                ref.ref_rmsnorm_sparse_residual_x(_p(x), _p(gamma), _p(inv), _p(scale), m, n, k, _p(out[0]), _p(out[1]),
+                                                  _p(out[2]), _p(out[3]), _p(out[4]))
+
+            def ref_plain():
+                ref.ref_fused_sparse_residual_x(_p(x), m, n, k, _p(out[0]), _p(out[1]), None, _p(out[2]), _p(out[3]),
+                                                _p(out[4]))
+
+            def my_rms():
+                call("sharq_fused_rmsnorm_sparse_residual_quantize_x", dptr(x), dptr(gamma), eps, m, n, k, dptr(ws),
+                     ws.numel(), dptr(out[0]), dptr(out[1]), dptr(out[2]), dptr(out[3]), dptr(out[4]), dptr(scale),
+                     stream_ptr())
+
+            def my_scaled():
+                call("sharq_scaled_sparse_residual_quantize_x", dptr(x), m, n, k, dptr(ws), ws.numel(), dptr(out[0]),
+                     dptr(out[1]), dptr(out[2]), dptr(out[3]), dptr(out[4]), dptr(scale), stream_ptr())
+
+            def my_plain():
+                call("sharq_fused_sparse_residual_quantize_x", dptr(x), m, n, k, dptr(out[0]), dptr(out[1]), dptr(out[2]),
+                     dptr(out[3]), dptr(out[4]), stream_ptr())
+
+            t = {"ref_rmsnorm(stats+fused)": _time_us(ref_rms) if k // 32 <= 1024 else float("nan"),
+                 "my_rmsnorm(stats+fused)": _time_us(my_rms) if k // 32 <= 1024 else float("nan"),
+                 "ref_plain(fused only)": _time_us(ref_plain), "my_plain(fused only)": _time_us(my_plain),
+                 "my_scaled(amax+divide+fused)": _time_us(my_scaled)}
+            hbm_us = (m * k * 2 + sum(sizes)) / 6533.8e3
+            print(f"\nprepare M={m} K={k} us: " + " ".join(f"{a}={b:.1f}" for a, b in t.items())
+                  + f" | HBM floor {hbm_us:.1f}", flush=True)
