@@ -106,6 +106,30 @@ class ClockSampler:
 # this project's arm
 # ------------------------------------------------------------------------------------------------
 
+def kernel_breakdown(fn, reps: int = 2, top: int = 14):
+    """Device time per kernel over `reps` calls of fn (CUPTI activity records through
+    torch.profiler; works on graph replays).  Returns rows sorted by total time."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(reps):
+            fn()
+        torch.cuda.synchronize()
+    rows = {}
+    for ev in prof.events():
+        if ev.device_type.name != "CUDA":
+            continue
+        d = rows.setdefault(ev.name, [0, 0.0])
+        d[0] += 1
+        d[1] += ev.device_time if hasattr(ev, "device_time") else ev.cuda_time
+    total = sum(v[1] for v in rows.values()) or 1.0
+    out = [{"kernel": k[:90], "launches_per_step": round(v[0] / reps, 1), "us_per_step": round(v[1] / reps, 1),
+            "share": round(v[1] / total, 4)} for k, v in sorted(rows.items(), key=lambda kv: -kv[1][1])]
+    return {"kernel_us_per_step": round(total / reps, 1), "rows": out[:top]}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -174,12 +198,15 @@ def run_ours(args):
                     prep = lin.local.prepare_input(x[inp])
                 if timers is not None:
                     ev[1].record()
-                y = lin.local.apply_prepared(prep)
+                if gamma is None and timers is None:
+                    y = lin.apply_prepared_reduced(prep)  # GEMM + sum over ranks
+                else:
+                    y = lin.local.apply_prepared(prep)
                 if timers is not None:
                     ev[2].record()
                     timers.append((name, ev))
-                if gamma is None:
-                    y = lin.reduce(y)
+                    if gamma is None:
+                        y = lin.reduce(y)
         return y
 
     def barrier():
@@ -256,6 +283,7 @@ def run_ours(args):
     ms_e2e = timed(e2e_step, args.steps) / args.steps
     e2e_value = total_flops / (ms_e2e * 1e-3) / 1e12
     clocks = sampler.stop() if rank == 0 else None
+    breakdown = kernel_breakdown(run_step) if args.kernel_table else None
 
     # ---- roofline pass: one more step with events around every prepare and GEMM call
     timers = []
@@ -324,9 +352,14 @@ def run_ours(args):
         ms_prefill = timed((lambda: pg.replay()) if pg is not None else (lambda: model.prefill(ids)),
                            args.prefill_steps) / args.prefill_steps
         assert torch.isfinite(logits).all()
+        prefill_breakdown = None
+        if args.kernel_table:
+            prefill_breakdown = kernel_breakdown((lambda: pg.replay()) if pg is not None else (lambda: model.prefill(ids)))
         prefill = {"model": f"llama3-8b shape, {layers_n} layers, random init, tp{world}", "batch": 1, "seq_len": m,
                    "ms": round(ms_prefill, 3), "tokens_per_s": round(m / (ms_prefill * 1e-3), 1),
                    "launch": "eager" if pg is None else "one CUDA graph"}
+        if prefill_breakdown is not None:
+            prefill["kernel_breakdown"] = prefill_breakdown
         if pg is not None:
             pg.reset()
         del model
@@ -363,6 +396,8 @@ def run_ours(args):
         "gpu_launches": args.steps * layers_n * 12,
         "clocks": clocks,
     }
+    if breakdown is not None:
+        result["kernel_breakdown"] = breakdown
     if rank == 0:
         if world == 1:
             result["cpu_baseline"] = cpu_baseline(seconds=args.cpu_seconds)
@@ -380,6 +415,9 @@ def run_ours(args):
         graph = None
     torch.cuda.synchronize()
     if world > 1:
+        from sharq_b200.tp import release_sum_buffers
+
+        release_sum_buffers()
         dist.barrier()
         dist.destroy_process_group()
     watchdog.cancel()
@@ -494,6 +532,8 @@ def main():
     ap.add_argument("--prefill-steps", type=int, default=3, help="0 skips the whole-model prefill measurement")
     ap.add_argument("--compare", action="store_true", help="also time the prefill with dense NVFP4 and bf16 linears (1 GPU)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph replay")
+    ap.add_argument("--kernel-table", action="store_true",
+                    help="add per-kernel device time of one step (and of the prefill) to the JSON line")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -135,6 +135,26 @@ int sharq_fused_rmsnorm_sparse_residual_quantize_x_noalloc(const void *x_bf16, c
 int sharq_noalloc_max_rows(void);
 const char *sharq_noalloc_last_error(void);
 
+/* No counterpart in the reference (it has no tensor parallelism).  In-place sum, over the
+ * `world` GPUs of one NVSwitch domain, of a bf16 buffer that every rank holds at the same
+ * offset of a symmetric-memory allocation bound to an NVLink multicast object: the partial
+ * outputs of a row-parallel SharQ linear (o_proj, down_proj).  One kernel per rank: rank r
+ * reduces bytes [r, r+1) * n_bytes / world inside the switch (multimem.ld_reduce, fp32
+ * accumulation) and stores the rounded bf16 sums to every rank's copy (multimem.st).
+ *   multicast_data   multicast address of the buffer
+ *   rank_flag_ptrs   HOST array of `world` device pointers: rank p's flag area as mapped in
+ *                    this process (peer mapping; entry `rank` is the local one).  Each area
+ *                    holds sharq_allreduce_flag_bytes() bytes, zeroed once (on every rank,
+ *                    followed by a barrier) before the first call; afterwards it holds the
+ *                    kernels' barrier counters and must not be touched.
+ *   n_bytes          multiple of 16 * world; max_ctas: 0 = default.
+ * All ranks must make the same calls in the same order with the same sizes.  The kernels of
+ * the ranks wait for one another with bounded spins (about two seconds); a wait that runs
+ * out sets *error_flag non-zero.  world <= 16. */
+int sharq_allreduce_bf16_multimem(void *multicast_data, void *const *rank_flag_ptrs, int rank, int world,
+                                  size_t n_bytes, int max_ctas, int *error_flag, void *stream);
+size_t sharq_allreduce_flag_bytes(void);
+
 /* Test/tuning hook: force the GEMM kernel variant (0 = automatic; 128 or 256 = single-CTA kernel
  * with that tile width; 512 = CTA-pair kernel, 256 x 256 tile per pair).  Process-wide. */
 int sharq_set_gemm_tile_n(int tile_n);

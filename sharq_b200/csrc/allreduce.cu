@@ -1,0 +1,127 @@
+// Sum of the partial outputs of a row-parallel SharQ linear over the GPUs of one NVSwitch
+// domain, in place, in one kernel per GPU: every rank reduces its 1/world slice of the
+// buffer INSIDE the switch (multimem.ld_reduce on the multicast address adds the same
+// 16 bytes of every rank's copy, accumulating in fp32) and writes the rounded result back to
+// every rank's copy with one multicast store (multimem.st).  Each GPU therefore receives the
+// buffer once (its own slice reduced, the other slices broadcast) and sends 1/world of it.
+//
+// The reference has no tensor parallelism, so this kernel has no counterpart there.
+//
+// Synchronisation: CTA b of every rank meets CTA b of all other ranks at a flag barrier
+// before reading (all partial sums are complete: a rank's kernel only starts after its GEMM
+// on the same stream) and again after storing (all copies are complete, and nobody still
+// reads this rank's copy).  A flag is one 32-bit counter in the RECEIVER's memory per (CTA,
+// sender): the sender adds 1 with a one-way system-scope release reduction through the peer
+// mapping, the receiver waits until the counter reaches the number of barriers it has been
+// through, which it keeps in its own memory next to the flags.  All state is in device
+// memory, so a captured launch can be replayed.  Every spin is bounded: when the limit
+// passes the kernel records an error code and goes on (the result is then wrong, and the
+// host sees the code), it never hangs.
+#include <cstdint>
+
+#include "allreduce.cuh"
+
+namespace sharq {
+
+namespace {
+
+constexpr int kThreads = 512;
+constexpr int kUnroll = 4;
+constexpr long long kSpinLimitCycles = 4000000000LL;  // about two seconds
+
+struct AllReduceParams {
+  uint8_t *mc;                            // multicast address of the data
+  uint32_t *flags[kAllReduceMaxRanks];    // flags[p]: rank p's flag words as mapped here
+  int rank, world;
+  size_t slice_bytes;                     // bytes / world, multiple of 16
+  int *error_flag;
+};
+
+__device__ __forceinline__ void ld_reduce_bf16x8(const uint8_t *mc_addr, uint32_t (&v)[4]) {
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+               : "l"(mc_addr)
+               : "memory");
+}
+
+__device__ __forceinline__ void st_multicast_16(uint8_t *mc_addr, const uint32_t (&v)[4]) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v[0]), "r"(v[1]),
+               "r"(v[2]), "r"(v[3])
+               : "memory");
+}
+
+__device__ __forceinline__ void signal_add_release(uint32_t *flag) {
+  asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
+}
+
+__device__ __forceinline__ uint32_t load_acquire(const uint32_t *flag) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+  return v;
+}
+
+// All ranks' CTAs with this block index meet for the `epoch`-th time.  Threads 0..world-1
+// each talk to one rank.
+__device__ __forceinline__ void cross_rank_barrier(const AllReduceParams &p, uint32_t epoch, int code) {
+  __syncthreads();
+  if ((int)threadIdx.x < p.world) {
+    const int peer = threadIdx.x;
+    __threadfence_system();
+    signal_add_release(p.flags[peer] + (size_t)blockIdx.x * p.world + p.rank);
+    const uint32_t *recv = p.flags[p.rank] + (size_t)blockIdx.x * p.world + peer;
+    const long long t0 = clock64();
+    while ((int32_t)(load_acquire(recv) - epoch) < 0) {
+      if (clock64() - t0 > kSpinLimitCycles) {
+        atomicExch(p.error_flag, code);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kThreads) allreduce_multimem_kernel(const AllReduceParams p) {
+  // barriers this CTA index has been through so far (same on every rank)
+  uint32_t *my_epoch = p.flags[p.rank] + (size_t)kAllReduceMaxCtas * kAllReduceMaxRanks + blockIdx.x;
+  const uint32_t epoch = *my_epoch;
+  cross_rank_barrier(p, epoch + 1, 0x100 + 1);
+  uint8_t *base = p.mc + (size_t)p.rank * p.slice_bytes;
+  const size_t stride = (size_t)gridDim.x * kThreads * 16;
+  for (size_t off = ((size_t)blockIdx.x * kThreads + threadIdx.x) * 16; off < p.slice_bytes; off += kUnroll * stride) {
+    uint32_t v[kUnroll][4];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+      if (off + u * stride < p.slice_bytes) ld_reduce_bf16x8(base + off + u * stride, v[u]);
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+      if (off + u * stride < p.slice_bytes) st_multicast_16(base + off + u * stride, v[u]);
+  }
+  cross_rank_barrier(p, epoch + 2, 0x100 + 2);
+  if (threadIdx.x == 0) *my_epoch = epoch + 2;
+}
+
+}  // namespace
+
+size_t allreduce_flag_bytes() {
+  return ((size_t)kAllReduceMaxCtas * kAllReduceMaxRanks + kAllReduceMaxCtas) * sizeof(uint32_t);
+}
+
+cudaError_t run_allreduce_multimem(void *multicast_data, void *const *rank_flag_ptrs, int rank, int world, size_t bytes,
+                                   int max_ctas, int *error_flag, cudaStream_t stream) {
+  AllReduceParams p{};
+  p.mc = static_cast<uint8_t *>(multicast_data);
+  for (int i = 0; i < world; ++i) p.flags[i] = static_cast<uint32_t *>(rank_flag_ptrs[i]);
+  p.rank = rank;
+  p.world = world;
+  p.slice_bytes = bytes / world;
+  p.error_flag = error_flag;
+  const size_t per_cta = (size_t)kThreads * 16 * kUnroll;
+  size_t ctas = (p.slice_bytes + per_cta - 1) / per_cta;
+  if (max_ctas <= 0 || max_ctas > kAllReduceMaxCtas) max_ctas = kAllReduceDefaultCtas;
+  if (ctas > (size_t)max_ctas) ctas = max_ctas;
+  if (ctas < 1) ctas = 1;
+  allreduce_multimem_kernel<<<(unsigned)ctas, kThreads, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace sharq

@@ -6,6 +6,7 @@
 #include <cstdio>
 #include <cstring>
 
+#include "allreduce.cuh"
 #include "common.cuh"
 #include "gemm.cuh"
 #include "prepare.cuh"
@@ -149,6 +150,21 @@ int sharq_compress_sparse_a(const void *a_q_dense, int m, int n, int k, void *a_
   SHARQ_REQUIRE(k % 32 == 0, "compress_sparse_a requires K to be a multiple of 32, got %d", k);
   SHARQ_REQUIRE(a_q_dense && a_comp && e, "null buffer");
   return check_cuda(sharq::run_compress_sparse_a(a_q_dense, m, k, a_comp, e, as_stream(stream)), "compress_sparse_a");
+}
+
+size_t sharq_allreduce_flag_bytes(void) { return sharq::allreduce_flag_bytes(); }
+
+int sharq_allreduce_bf16_multimem(void *multicast_data, void *const *rank_flag_ptrs, int rank, int world,
+                                  size_t n_bytes, int max_ctas, int *error_flag, void *stream) {
+  SHARQ_REQUIRE(multicast_data && rank_flag_ptrs && error_flag, "multicast_data, rank_flag_ptrs, error_flag must be set");
+  SHARQ_REQUIRE(world >= 1 && world <= sharq::kAllReduceMaxRanks, "world must be in [1, %d]", sharq::kAllReduceMaxRanks);
+  SHARQ_REQUIRE(rank >= 0 && rank < world, "rank must be in [0, world)");
+  SHARQ_REQUIRE(n_bytes > 0 && n_bytes % ((size_t)16 * world) == 0, "n_bytes must be a positive multiple of 16 * world");
+  SHARQ_REQUIRE((reinterpret_cast<uintptr_t>(multicast_data) & 15) == 0, "multicast_data must be 16-byte aligned");
+  for (int i = 0; i < world; ++i) SHARQ_REQUIRE(rank_flag_ptrs[i] != nullptr, "rank_flag_ptrs[%d] is NULL", i);
+  return check_cuda(sharq::run_allreduce_multimem(multicast_data, rank_flag_ptrs, rank, world, n_bytes, max_ctas,
+                                                  error_flag, as_stream(stream)),
+                    "allreduce_multimem launch");
 }
 
 int sharq_set_gemm_tile_n(int tile_n) {

@@ -376,17 +376,23 @@ def sparse_matmul_tensor_scale(A_comp, B, E, SFA, SFB, M: int, N: int, K: int, a
 
 
 def sharq_linear_gemm(A_comp, E, SFA_sparse, Q_res, SF_res, QW, SFW_sparse, SFW_dense, alpha,
-                      bias: Optional[torch.Tensor] = None, alpha_host: float = 1.0) -> torch.Tensor:
+                      bias: Optional[torch.Tensor] = None, alpha_host: float = 1.0,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Fused sparse-main + dense-residual GEMM on a prepared activation (one launch).
     alpha: python float or 1-element CUDA float32 tensor; the factor applied is
-    alpha * alpha_host."""
+    alpha * alpha_host.  out: optional contiguous bf16 [M, N] tensor to write into."""
     M, K = int(Q_res.shape[0]), int(Q_res.shape[1]) * 2
     N = int(QW.shape[0])
     dev = Q_res.device
     if bias is not None:
         _check(bias.is_cuda and bias.dtype == torch.bfloat16 and bias.numel() == N and bias.is_contiguous(),
                "bias must be a contiguous CUDA bfloat16 tensor with N elements")
-    D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    if out is None:
+        D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    else:
+        _check(out.is_cuda and out.device == dev and out.dtype == torch.bfloat16 and out.is_contiguous()
+               and tuple(out.shape) == (M, N), "out must be a contiguous CUDA bfloat16 tensor shaped [M, N]")
+        D = out
     alpha_t = alpha if isinstance(alpha, torch.Tensor) else None
     with _on_device(dev):
         _lib.check(_lib.lib().sharq_linear_gemm(

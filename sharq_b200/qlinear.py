@@ -107,14 +107,18 @@ class QLinearLayer(nn.Module):
         return self.prepare_input(x_norm, out_features_hint=out_features_hint)
 
     @torch.no_grad()
-    def apply_prepared(self, prepared):
+    def apply_prepared(self, prepared, out=None):
+        """out: optional bf16 [M, N] tensor the fused SharQ GEMM writes into (used by the
+        tensor-parallel layers to place partial sums in symmetric memory)."""
         tag = prepared[0]
+        if out is not None and not (tag == "SHARQ" and self.fused_gemm):
+            raise ValueError("out= is only supported by the fused SharQ GEMM")
         if tag == "SHARQ":
             _, a_comp, e, sfa, q_res, sf_res, scale_x = prepared
             if self.fused_gemm:
                 return ops.sharq_linear_gemm(a_comp, e, sfa, q_res, sf_res, self.weight_q, self.scale_w_sparse,
                                              self.scale_w_dense, scale_x.reshape(1), bias=self.bias,
-                                             alpha_host=self.weight_scale_host)
+                                             alpha_host=self.weight_scale_host, out=out)
             output_scale = (scale_x * self.weight_scale).reshape(1).contiguous()
             y_sparse = ops.sparse_matmul_tensor_scale(a_comp, self.weight_q, e, sfa, self.scale_w_sparse,
                                                       q_res.shape[0], self.out_features, self.in_features,

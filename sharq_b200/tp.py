@@ -15,9 +15,19 @@ layer consistent with the single-GPU layer:
 * row-parallel layers (o_proj, down_proj) shard K; each rank prepares its own K-slice of
   the activation with its own tensor scale and produces a partial sum in bf16; the partial
   sums are all-reduced; the bias is added once, after the reduce.
+
+The all-reduce of a row-parallel layer on GPUs is this project's own kernel
+(csrc/allreduce.cu): the GEMM writes its partial sums straight into a buffer in symmetric
+memory (allocated and exchanged through torch.distributed._symmetric_memory, which is
+plumbing here) and one kernel per rank reduces them inside the NVSwitch (multimem.ld_reduce
+/ multimem.st).  SHARQ_TP_ALLREDUCE=nccl selects torch.distributed's all_reduce instead;
+process groups without CUDA multicast support (the gloo groups of the CPU tests) always use
+it.
 """
 from __future__ import annotations
 
+import ctypes
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -50,6 +60,105 @@ def scaled_weight(weight: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """Full weight divided by its global tensor scale (bf16), and that scale."""
     scale = torch.clamp(weight.abs().max().float() / (448.0 * 6.0), min=1e-9)
     return (weight / scale).to(torch.bfloat16), scale
+
+
+class SymmetricSumBuffer:
+    """bf16 scratch in symmetric memory for the partial sums of row-parallel layers, shared
+    by all layers of a process group: SLOTS equal slots used round-robin, so the result of
+    one row-parallel layer stays valid until SLOTS more have run.  Construction and growth
+    are collective (every rank must do them at the same point, outside stream capture)."""
+
+    SLOTS = 2
+
+    def __init__(self, slot_bytes: int, group, device: torch.device):
+        import torch.distributed._symmetric_memory as symm
+
+        from . import _lib
+
+        lib = _lib.lib()
+        self.group, self.device = group, device
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.slot_bytes = (int(slot_bytes) + 4095) // 4096 * 4096
+        flag_bytes = int(lib.sharq_allreduce_flag_bytes())
+        self.storage = symm.empty(self.SLOTS * self.slot_bytes + flag_bytes, dtype=torch.uint8, device=device)
+        handle = symm.rendezvous(self.storage, group.group_name)
+        if not int(handle.multicast_ptr):
+            raise RuntimeError("symmetric memory has no NVLink multicast mapping on this system")
+        offset = int(getattr(handle, "offset", 0))
+        bases = [int(p) + offset for p in handle.buffer_ptrs]
+        if bases[self.rank] != self.storage.data_ptr():
+            raise RuntimeError("symmetric-memory handle does not describe the tensor it was made from")
+        self.multicast = int(handle.multicast_ptr) + offset
+        self.storage.zero_()  # the barrier counters in the flag area start at zero
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+        flags_at = self.SLOTS * self.slot_bytes
+        self.flag_ptrs = (ctypes.c_void_p * self.world)(*[b + flags_at for b in bases])
+        self.handle = handle
+        self._next = 0
+
+    def take(self, m: int, n: int) -> Tuple[int, torch.Tensor]:
+        """Next slot and a bf16 [m, n] view of it."""
+        slot = self._next
+        self._next = (slot + 1) % self.SLOTS
+        begin = slot * self.slot_bytes
+        return slot, self.storage[begin:begin + m * n * 2].view(torch.bfloat16).view(m, n)
+
+    def sum_(self, slot: int, nbytes: int, max_ctas: int = 0) -> None:
+        """Enqueue the in-switch all-reduce of the first nbytes of `slot` on the current stream
+        (max_ctas: 0 = the library's default grid limit)."""
+        from . import _lib, ops
+
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().sharq_allreduce_bf16_multimem(
+                ctypes.c_void_p(self.multicast + slot * self.slot_bytes), self.flag_ptrs, self.rank, self.world, nbytes,
+                int(max_ctas),
+                ctypes.c_void_p(ops._error_flag(self.device).data_ptr()),
+                ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)))
+
+
+_SUM_BUFFERS = {}
+
+
+def _multimem_wanted(group) -> bool:
+    mode = os.environ.get("SHARQ_TP_ALLREDUCE", "auto").lower()
+    if mode not in ("auto", "multimem", "nccl"):
+        raise ValueError("SHARQ_TP_ALLREDUCE must be auto, multimem or nccl")
+    if mode == "nccl":
+        return False
+    usable = torch.cuda.is_available() and dist.get_backend(group) == "nccl"
+    if mode == "multimem" and not usable:
+        raise RuntimeError("SHARQ_TP_ALLREDUCE=multimem needs CUDA devices and an NCCL process group")
+    return usable
+
+
+def sum_buffer(group, device: torch.device, nbytes: int) -> Optional[SymmetricSumBuffer]:
+    """The group's shared SymmetricSumBuffer with slots of at least nbytes (collective when it
+    has to be created or grown), or None when the in-switch all-reduce is not in use."""
+    group = group if group is not None else dist.group.WORLD
+    key = (group.group_name, device.index)
+    if key in _SUM_BUFFERS and _SUM_BUFFERS[key] is None:
+        return None
+    buf = _SUM_BUFFERS.get(key)
+    if buf is None or buf.slot_bytes < nbytes:
+        if buf is None and not _multimem_wanted(group):
+            _SUM_BUFFERS[key] = None
+            return None
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("the symmetric sum buffer must be created before stream capture: run the layer once first")
+        try:
+            buf = SymmetricSumBuffer(nbytes, group, device)
+        except RuntimeError:
+            if os.environ.get("SHARQ_TP_ALLREDUCE", "auto").lower() == "multimem":
+                raise
+            buf = None  # no multicast on this system: torch.distributed's all_reduce is used
+        _SUM_BUFFERS[key] = buf
+    return buf
+
+
+def release_sum_buffers() -> None:
+    """Drop the shared symmetric buffers (call before destroying the process group)."""
+    _SUM_BUFFERS.clear()
 
 
 class _ShardedBase(nn.Module):
@@ -114,8 +223,29 @@ class RowParallelSharqLinear(_ShardedBase):
             y_partial = y_partial + self.bias
         return y_partial
 
+    def apply_prepared_reduced(self, prepared) -> torch.Tensor:
+        """GEMM on a prepared K-slice and the sum over ranks.  On GPUs with NVLink multicast
+        the partial sums go straight into symmetric memory and are reduced in the switch; the
+        returned tensor is then a view of a shared slot (valid until SymmetricSumBuffer.SLOTS
+        more row-parallel layers of the group have run)."""
+        if self.world == 1:
+            return self.reduce(self.local.apply_prepared(prepared))
+        m, n = int(prepared[4].shape[0]) if prepared[0] == "SHARQ" else 0, self.local.out_features
+        nbytes = m * n * 2
+        buf = None
+        if prepared[0] == "SHARQ" and self.local.fused_gemm and nbytes > 0 and nbytes % (16 * self.world) == 0:
+            buf = sum_buffer(self.group, prepared[4].device, nbytes)
+        if buf is None:
+            return self.reduce(self.local.apply_prepared(prepared))
+        slot, view = buf.take(m, n)
+        self.local.apply_prepared(prepared, out=view)
+        buf.sum_(slot, nbytes)
+        return view + self.bias if self.bias is not None else view
+
     def forward(self, x_local):
-        return self.reduce(self.local(x_local))
+        x2 = x_local.reshape(-1, x_local.shape[-1]).to(torch.bfloat16)
+        y = self.apply_prepared_reduced(self.local.prepare_input(x2))
+        return y.reshape(*x_local.shape[:-1], y.shape[-1])
 
 
 def all_reduce_sum_(t: torch.Tensor, group=None) -> torch.Tensor:
