@@ -42,6 +42,9 @@ namespace {
 constexpr int kBM = 128;
 constexpr int kBK = 256;  // logical K per stage
 constexpr int kEpiWarps = 8;
+// Optional instrumentation build (-DSHARQ_GEMM_TIMING): cycles the producer and MMA threads
+// spend in each wait and issue phase, summed into g_timing and read by
+// sharq_debug_read_timing().  Off in the shipped library.
 #ifdef SHARQ_GEMM_TIMING
 __device__ unsigned long long g_timing[8];
 #define TIMING_T0() long long t0_ = clock64()
@@ -242,13 +245,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const int n_d = DENSE ? min(4, tiles_d - 4 * it) : 0;
           uint32_t tx = L::kWBytes + L::kADenseBytes + L::kACompBytes + L::kEBytes;
           tx += (uint32_t)(n_sp * 512 * (1 + L::kBands) + n_d * 512 * (1 + L::kBands));
-#ifdef SHARQ_GEMM_NOLOAD
-          // debug experiment: after the first pass over the ring, re-arm the stage without copying
-          if (g >= (uint32_t)S) {
-            ptx::mbar_arrive(full_bar + s);
-            continue;
-          }
-#endif
           ptx::mbar_arrive_expect_tx(full_bar + s, tx);
           ptx::tma_load_2d(st + L::kOffW, &tm_w, it * 128, w_row, full_bar + s);
           if (DENSE) {
@@ -592,13 +588,30 @@ cudaError_t run_gemm(const GemmArgs &a, cudaStream_t stream) {
   const bool dense = a.a_dense != nullptr;
   if (!sparse && !dense) return cudaErrorInvalidValue;
   // tile_n: 0 = automatic, 128 / 256 = single-CTA tiles of that width, 512 = CTA pairs (256 x 256)
-  const bool pair = a.tile_n == 512 || (a.tile_n == 0 && a.m > 128 && a.n > 128);
+  int tile_n = a.tile_n;
+  if (tile_n == 0) {
+    int dev = 0, sms = 0;
+    cudaError_t e = device_info(&dev, &sms);
+    if (e != cudaSuccess) return e;
+    const int pair_units = ((a.m + 255) / 256) * ((a.n + 255) / 256);
+    if (a.m <= 128 || a.n <= 128) {
+      tile_n = a.n > 128 ? 256 : 128;
+    } else if (pair_units * 4 <= sms || a.k <= 512) {
+      // 256 x 256 pair tiles would keep at most half of the SMs busy, or the K loop is too
+      // short to hide the drain of a 256-wide accumulator: 128 x 128 tiles (measured at the
+      // 8-way tensor-parallel shapes: 14.6 vs 18.8 us for N = 768, 12.7 vs 16.7 us for K = 512)
+      tile_n = 128;
+    } else {
+      tile_n = 512;
+    }
+  }
+  const bool pair = tile_n == 512;
   if (pair) {
     if (sparse && dense) return launch<256, true, true, true>(a, stream);
     if (sparse) return launch<256, true, false, true>(a, stream);
     return launch<256, false, true, true>(a, stream);
   }
-  const int bn = a.tile_n == 128 ? 128 : (a.tile_n == 256 ? 256 : (a.n > 128 ? 256 : 128));
+  const int bn = tile_n == 128 ? 128 : 256;
   if (bn == 256) {
     if (sparse && dense) return launch<256, true, true, false>(a, stream);
     if (sparse) return launch<256, true, false, false>(a, stream);

@@ -131,11 +131,6 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *m, int
       : "memory");
 }
 
-// Pull one tile of a tensor map into L2 without touching shared memory.
-__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap *m, int c0, int c1) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(m), "r"(c0), "r"(c1) : "memory");
-}
-
 // Plain 1-D bulk copy global -> shared (16-byte aligned addresses, size multiple of 16).
 __device__ __forceinline__ void bulk_load_1d(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
