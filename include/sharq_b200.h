@@ -75,6 +75,31 @@ int sharq_scaled_sparse_residual_quantize_x(const void *x_bf16, int m, int n, in
                                             size_t workspace_bytes, void *a_comp, void *e, void *sfa_sparse,
                                             void *q_res, void *sf_res, float *scale_out, void *stream);
 
+/* Decoder-layer steps between the SharQ linears, which the reference leaves to
+ * HuggingFace's PyTorch code; each intermediate is rounded to bf16 where the PyTorch
+ * composition rounds, so the results are those of the ATen ops.
+ *
+ * sharq_rope_inplace: rotary embedding x*cos + rotate_half(x)*sin, in place, on the first
+ * `heads` heads of every row of a bf16 matrix (the query and key heads of a merged qkv
+ * activation); row_stride in elements; position of a row = row % seq_len; cos/sin are bf16
+ * [seq_len, head_dim].  Stands behind apply_rotary_pos_emb at model/qLlamaLayer.py:137-141.
+ *
+ * sharq_swiglu: H[rows, ffn] = silu(gate) * up of a contiguous merged activation
+ * gate_up[rows, 2*ffn] (gate columns first).  model/qLlamaLayer.py:183-185.
+ *
+ * sharq_swiglu_sparse_residual_quantize_x: the same H (written to h_bf16, [M, K]) and the
+ * scaled prepare of H for down_proj in two launches instead of the reference's five passes
+ * (silu, mul, amax, divide, prepare): the SwiGLU kernel leaves max|H| in the workspace, so
+ * the statistics pass of sharq_scaled_sparse_residual_quantize_x is not needed.  Outputs
+ * equal sharq_scaled_sparse_residual_quantize_x(H). */
+int sharq_rope_inplace(void *x_bf16, int rows, int row_stride, int seq_len, int heads, int head_dim,
+                       const void *cos_bf16, const void *sin_bf16, void *stream);
+int sharq_swiglu(const void *gate_up_bf16, int rows, int ffn, void *h_bf16, void *stream);
+int sharq_swiglu_sparse_residual_quantize_x(const void *gate_up_bf16, int m, int n, int k, void *h_bf16,
+                                            void *workspace, size_t workspace_bytes, void *a_comp, void *e,
+                                            void *sfa_sparse, void *q_res, void *sf_res, float *scale_out,
+                                            void *stream);
+
 /* quantize_w32_shared(W): bf16 [N,K] (already divided by the weight tensor scale),
  * K % 32 == 0 -> QW [N,K/2], SFW_sparse (32-groups), SFW_dense (each scale duplicated
  * into two 16-group slots).  bindings.cpp:392-417 */

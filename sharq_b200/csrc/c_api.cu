@@ -8,6 +8,7 @@
 
 #include "allreduce.cuh"
 #include "common.cuh"
+#include "decoder_ops.cuh"
 #include "gemm.cuh"
 #include "prepare.cuh"
 #include "quant.cuh"
@@ -116,6 +117,43 @@ int sharq_scaled_sparse_residual_quantize_x(const void *x, int m, int n, int k, 
   return check_cuda(sharq::run_scaled_prepare(x, nullptr, 0.0f, m, k, workspace, nullptr, a_comp, e, sfa_sparse, q_res,
                                               sf_res, scale_out, as_stream(stream)),
                     "scaled_sparse_residual_quantize_x");
+}
+
+int sharq_rope_inplace(void *x_bf16, int rows, int row_stride, int seq_len, int heads, int head_dim, const void *cos_bf16,
+                       const void *sin_bf16, void *stream) {
+  SHARQ_REQUIRE(x_bf16 && cos_bf16 && sin_bf16, "null buffer");
+  SHARQ_REQUIRE(rows > 0 && seq_len > 0 && heads > 0, "rows, seq_len, heads must be positive");
+  SHARQ_REQUIRE(head_dim > 0 && head_dim % 16 == 0, "head_dim must be a positive multiple of 16, got %d", head_dim);
+  SHARQ_REQUIRE(row_stride >= heads * head_dim && row_stride % 8 == 0,
+                "row_stride must cover heads * head_dim and be a multiple of 8");
+  SHARQ_REQUIRE((reinterpret_cast<uintptr_t>(x_bf16) & 15) == 0, "x must be 16-byte aligned");
+  return check_cuda(sharq::run_rope_inplace(x_bf16, rows, row_stride, seq_len, heads, head_dim, cos_bf16, sin_bf16,
+                                            as_stream(stream)),
+                    "rope_inplace");
+}
+
+int sharq_swiglu(const void *gate_up_bf16, int rows, int ffn, void *h_bf16, void *stream) {
+  SHARQ_REQUIRE(gate_up_bf16 && h_bf16, "null buffer");
+  SHARQ_REQUIRE(rows > 0 && ffn > 0 && ffn % 8 == 0, "rows must be positive and ffn a positive multiple of 8");
+  return check_cuda(sharq::run_swiglu_absmax(gate_up_bf16, rows, ffn, 2LL * ffn, h_bf16, nullptr, as_stream(stream)),
+                    "swiglu");
+}
+
+int sharq_swiglu_sparse_residual_quantize_x(const void *gate_up_bf16, int m, int n, int k, void *h_bf16, void *workspace,
+                                            size_t workspace_bytes, void *a_comp, void *e, void *sfa_sparse, void *q_res,
+                                            void *sf_res, float *scale_out, void *stream) {
+  (void)n;
+  SHARQ_REQUIRE(m > 0 && k > 0, "gate_up must be shaped [M, 2K]");
+  SHARQ_REQUIRE(k % 128 == 0, "swiglu_sparse_residual_quantize_x requires K to be a multiple of 128, got %d", k);
+  SHARQ_REQUIRE(gate_up_bf16 && h_bf16 && a_comp && e && sfa_sparse && q_res && sf_res, "null buffer");
+  SHARQ_REQUIRE(workspace && workspace_bytes >= 256, "workspace too small: need 256 bytes");
+  if (check_cuda(sharq::run_swiglu_absmax(gate_up_bf16, m, k, 2LL * k, h_bf16, static_cast<unsigned int *>(workspace),
+                                          as_stream(stream)),
+                 "swiglu_absmax"))
+    return 1;
+  return check_cuda(sharq::run_scaled_prepare(h_bf16, nullptr, 0.0f, m, k, workspace, nullptr, a_comp, e, sfa_sparse,
+                                              q_res, sf_res, scale_out, as_stream(stream), /*absmax_ready=*/true),
+                    "swiglu_sparse_residual_quantize_x");
 }
 
 int sharq_quantize_w32_shared(const void *w, int n, int k, void *qw, void *sfw_sparse, void *sfw_dense, void *stream) {

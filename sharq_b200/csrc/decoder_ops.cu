@@ -1,0 +1,159 @@
+// Element-wise steps of a decoder layer that sit between the SharQ linears, as single
+// kernels for sm_100a.  The reference leaves both to HuggingFace's PyTorch code
+// (model/qLlamaLayer.py:137-141 rotary embedding, :183-185 act_fn(gate) * up); as ATen ops on
+// strided views they cost more than the quantised GEMMs they connect, so the prefill path
+// runs them here.  Every intermediate is rounded to bf16 exactly where the PyTorch
+// composition rounds, so results are those of the ATen ops.
+//
+//   rope_inplace      x*cos + rotate_half(x)*sin on the query and key heads of a merged
+//                     qkv activation, in place: bf16(bf16(x*cos) + bf16(rot*sin))
+//   swiglu_absmax     h = bf16(bf16(silu(gate)) * up) from a merged gate_up activation, plus
+//                     the tensor-wide max|h| the scaled prepare of down_proj needs, so that
+//                     prepare does not have to read h a second time for it
+#include <cuda_bf16.h>
+
+#include <cstdint>
+
+#include "decoder_ops.cuh"
+
+namespace sharq {
+
+namespace {
+
+__device__ __forceinline__ float lo_f(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float hi_f(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+
+// one element of the rotary embedding: bf16(bf16(x * c) + bf16(r * s))
+__device__ __forceinline__ float rope1(float x, float r, float c, float s) {
+  return round_bf16(__fmul_rn(x, c)) + round_bf16(__fmul_rn(r, s));
+}
+
+// A thread rotates 8 elements of the first half of a head with their 8 partners in the
+// second half (rotate_half pairs element d with d + D/2).
+__global__ void __launch_bounds__(256) rope_kernel(__nv_bfloat16 *__restrict__ x, long long rows, long long row_stride,
+                                                   int seq_len, int heads, int head_dim,
+                                                   const __nv_bfloat16 *__restrict__ cos_t,
+                                                   const __nv_bfloat16 *__restrict__ sin_t) {
+  const int half = head_dim >> 1;
+  const int vecs = half >> 3;  // 16-byte vectors per half head
+  const long long total = rows * heads * vecs;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int v = (int)(i % vecs);
+    const long long rh = i / vecs;
+    const int head = (int)(rh % heads);
+    const long long row = rh / heads;
+    const int pos = (int)(row % seq_len);
+    __nv_bfloat16 *p = x + row * row_stride + (long long)head * head_dim + v * 8;
+    const __nv_bfloat16 *c = cos_t + (long long)pos * head_dim + v * 8;
+    const __nv_bfloat16 *s = sin_t + (long long)pos * head_dim + v * 8;
+    const uint4 a4 = *reinterpret_cast<const uint4 *>(p);
+    const uint4 b4 = *reinterpret_cast<const uint4 *>(p + half);
+    const uint4 ca4 = __ldg(reinterpret_cast<const uint4 *>(c));
+    const uint4 cb4 = __ldg(reinterpret_cast<const uint4 *>(c + half));
+    const uint4 sa4 = __ldg(reinterpret_cast<const uint4 *>(s));
+    const uint4 sb4 = __ldg(reinterpret_cast<const uint4 *>(s + half));
+    const uint32_t a[4] = {a4.x, a4.y, a4.z, a4.w}, b[4] = {b4.x, b4.y, b4.z, b4.w};
+    const uint32_t ca[4] = {ca4.x, ca4.y, ca4.z, ca4.w}, cb[4] = {cb4.x, cb4.y, cb4.z, cb4.w};
+    const uint32_t sa[4] = {sa4.x, sa4.y, sa4.z, sa4.w}, sb[4] = {sb4.x, sb4.y, sb4.z, sb4.w};
+    uint32_t oa[4], ob[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      // first half: x*cos + (-partner)*sin ; second half: x*cos + partner*sin
+      oa[j] = pack2(rope1(lo_f(a[j]), -lo_f(b[j]), lo_f(ca[j]), lo_f(sa[j])),
+                    rope1(hi_f(a[j]), -hi_f(b[j]), hi_f(ca[j]), hi_f(sa[j])));
+      ob[j] = pack2(rope1(lo_f(b[j]), lo_f(a[j]), lo_f(cb[j]), lo_f(sb[j])),
+                    rope1(hi_f(b[j]), hi_f(a[j]), hi_f(cb[j]), hi_f(sb[j])));
+    }
+    *reinterpret_cast<uint4 *>(p) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+    *reinterpret_cast<uint4 *>(p + half) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+  }
+}
+
+// silu as ATen computes it for a bf16 tensor: x / (1 + exp(-x)) in float, rounded to bf16
+__device__ __forceinline__ float silu_bf16(float x) { return round_bf16(x / (1.0f + expf(-x))); }
+
+__global__ void __launch_bounds__(256) swiglu_absmax_kernel(const __nv_bfloat16 *__restrict__ gate_up, long long rows,
+                                                            int ffn, long long row_stride, __nv_bfloat16 *__restrict__ h,
+                                                            unsigned int *__restrict__ amax_bits) {
+  __shared__ float warp_max[8];
+  const int vecs = ffn >> 3;
+  const long long total = rows * vecs;
+  float mx = 0.0f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / vecs;
+    const int v = (int)(i % vecs);
+    const __nv_bfloat16 *g = gate_up + row * row_stride + v * 8;
+    const uint4 g4 = __ldg(reinterpret_cast<const uint4 *>(g));
+    const uint4 u4 = __ldg(reinterpret_cast<const uint4 *>(g + ffn));
+    const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = round_bf16(__fmul_rn(silu_bf16(lo_f(gw[j])), lo_f(uw[j])));
+      const float b = round_bf16(__fmul_rn(silu_bf16(hi_f(gw[j])), hi_f(uw[j])));
+      mx = fmaxf(mx, fmaxf(fabsf(a), fabsf(b)));
+      o[j] = pack2(a, b);
+    }
+    *reinterpret_cast<uint4 *>(h + row * (long long)ffn + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) warp_max[warp] = mx;
+  __syncthreads();
+  if (warp == 0) {
+    mx = lane < 8 ? warp_max[lane] : 0.0f;
+#pragma unroll
+    for (int off = 4; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    // non-negative floats order like their bit patterns
+    if (lane == 0 && amax_bits != nullptr) atomicMax(amax_bits, __float_as_uint(mx));
+  }
+}
+
+int sm_count() {
+  static int sms[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (sms[dev] == 0 && cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms[dev] = 148;
+  return sms[dev];
+}
+
+unsigned grid_for(long long work_items) {
+  long long blocks = (work_items + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (unsigned)blocks;
+}
+
+}  // namespace
+
+cudaError_t run_rope_inplace(void *x, long long rows, long long row_stride, int seq_len, int heads, int head_dim,
+                             const void *cos_t, const void *sin_t, cudaStream_t stream) {
+  const long long items = rows * heads * (head_dim / 16);
+  rope_kernel<<<grid_for(items), 256, 0, stream>>>(static_cast<__nv_bfloat16 *>(x), rows, row_stride, seq_len, heads,
+                                                   head_dim, static_cast<const __nv_bfloat16 *>(cos_t),
+                                                   static_cast<const __nv_bfloat16 *>(sin_t));
+  return cudaGetLastError();
+}
+
+cudaError_t run_swiglu_absmax(const void *gate_up, long long rows, int ffn, long long row_stride, void *h,
+                              unsigned int *amax_bits, cudaStream_t stream) {
+  if (amax_bits != nullptr) {
+    cudaError_t err = cudaMemsetAsync(amax_bits, 0, sizeof(unsigned int), stream);
+    if (err != cudaSuccess) return err;
+  }
+  const long long items = rows * (ffn / 8);
+  swiglu_absmax_kernel<<<grid_for(items), 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(gate_up), rows, ffn,
+                                                            row_stride, static_cast<__nv_bfloat16 *>(h), amax_bits);
+  return cudaGetLastError();
+}
+
+}  // namespace sharq

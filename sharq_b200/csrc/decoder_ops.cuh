@@ -1,0 +1,17 @@
+// Host launchers of the decoder-layer element-wise kernels (decoder_ops.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+namespace sharq {
+
+// Rotary embedding in place on `heads` consecutive heads at the start of every row of a bf16
+// matrix (row_stride elements between rows); position = row % seq_len; cos/sin: [seq_len, head_dim].
+cudaError_t run_rope_inplace(void *x, long long rows, long long row_stride, int seq_len, int heads, int head_dim,
+                             const void *cos_t, const void *sin_t, cudaStream_t stream);
+
+// h[rows, ffn] = silu(gate) * up from gate_up[rows, 2*ffn] (gate first); amax_bits (optional) is
+// zeroed and then raised to the bits of max|h|.
+cudaError_t run_swiglu_absmax(const void *gate_up, long long rows, int ffn, long long row_stride, void *h,
+                              unsigned int *amax_bits, cudaStream_t stream);
+
+}  // namespace sharq

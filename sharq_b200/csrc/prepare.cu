@@ -537,15 +537,19 @@ cudaError_t run_prepare(const void *x, int m, int k, void *a_comp, void *e, void
 
 cudaError_t run_scaled_prepare(const void *x, const void *gamma, float eps, int m, int k, void *workspace,
                                float *inv_rms_external, void *a_comp, void *e, void *sfa_sparse, void *q_res,
-                               void *sf_res, float *scale_out, cudaStream_t stream) {
+                               void *sf_res, float *scale_out, cudaStream_t stream, bool absmax_ready) {
   // workspace: [0,4) tensor absmax bits; [256, 256+4m) inv_rms
   auto *amax_bits = static_cast<unsigned int *>(workspace);
   float *inv_rms = inv_rms_external ? inv_rms_external
                                     : reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + 256);
-  cudaError_t err = cudaMemsetAsync(amax_bits, 0, sizeof(unsigned int), stream);
-  if (err != cudaSuccess) return err;
+  cudaError_t err = cudaSuccess;
   const bool rms = gamma != nullptr;
-  if (rms) {
+  if (absmax_ready) {
+    // the producer of x already left max|x| in the workspace: no statistics pass
+    if (rms) return cudaErrorInvalidValue;
+  } else if ((err = cudaMemsetAsync(amax_bits, 0, sizeof(unsigned int), stream)) != cudaSuccess) {
+    return err;
+  } else if (rms) {
     const int groups = k / 32;
     const int threads = (groups + 31) / 32 * 32;
     rms_stats_kernel<<<m, threads, (size_t)groups * sizeof(float), stream>>>(

@@ -10,8 +10,11 @@ decoder with the same call pattern on the quantized path:
 * the input and post-attention RMSNorms are fused into the prepare of the following
   linears; the decoder layer never runs them separately - model/qLlamaLayer.py:219-221
 * o_proj and down_proj take the plain (non-RMSNorm) prepare
-* attention itself is stock `scaled_dot_product_attention` with RoPE and grouped KV heads;
-  it is not part of the accelerated path.
+* attention itself is stock `scaled_dot_product_attention` with grouped KV heads; it is not
+  part of the accelerated path.  The rotary embedding runs in place on the merged qkv output
+  (one kernel, ops.rope_inplace_) and SwiGLU is fused with the prepare of down_proj
+  (prepare_input_swiglu); both give the bits of the ATen compositions they replace, which
+  `fused_glue=False` still runs.
 
 Tensor parallelism (`world` > 1): attention heads and the FFN width are sharded; qkv and
 gate_up are column-parallel, o_proj and down_proj row-parallel with an all-reduce.
@@ -66,8 +69,9 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
 
 class SharqDecoderLayer(torch.nn.Module):
     def __init__(self, cfg: DecoderConfig, gen: torch.Generator, device, world: int = 1, rank: int = 0,
-                 keep_reference: bool = False, mode: str = "SHARQ"):
+                 keep_reference: bool = False, mode: str = "SHARQ", fused_glue: bool = True):
         super().__init__()
+        self.fused_glue = fused_glue
         if mode not in ("SHARQ", "NVFP4", "BF16"):
             raise ValueError(f"unknown mode {mode}")
         if mode != "SHARQ" and world != 1:
@@ -122,6 +126,8 @@ class SharqDecoderLayer(torch.nn.Module):
             self.qkv = self.o_proj = self.gate_up = self.down = None
         elif mode == "BF16":
             self.qkv = self.o_proj = self.gate_up = self.down = None
+            if fused_glue:  # one merged gate_up GEMM, as on the quantised paths
+                self.ref["gate_up"] = torch.cat((self.ref.pop("gate"), self.ref.pop("up")))
         self.input_norm = (1 + 0.1 * torch.randn(h, generator=gen, device=device)).to(torch.bfloat16)
         self.post_norm = (1 + 0.1 * torch.randn(h, generator=gen, device=device)).to(torch.bfloat16)
 
@@ -137,18 +143,17 @@ class SharqDecoderLayer(torch.nn.Module):
         x2 = x.reshape(b * s, h)
         prep = self.qkv.prepare_input_rmsnorm(x2, self.input_norm, cfg.eps)
         qkv = self.qkv.apply_prepared(prep)
-        nq, nk = self.local_heads * cfg.head_dim, self.local_kv * cfg.head_dim
-        q = qkv[:, :nq].view(b, s, self.local_heads, cfg.head_dim).transpose(1, 2)
-        k = qkv[:, nq:nq + nk].view(b, s, self.local_kv, cfg.head_dim).transpose(1, 2)
-        v = qkv[:, nq + nk:].view(b, s, self.local_kv, cfg.head_dim).transpose(1, 2)
-        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+        q, k, v = _split_heads(qkv, b, s, self.local_heads, self.local_kv, cfg.head_dim, cos, sin, self.fused_glue)
         attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
-        attn2 = attn.transpose(1, 2).reshape(b * s, nq)
+        attn2 = attn.transpose(1, 2).reshape(b * s, self.local_heads * cfg.head_dim)
         x2 = x2 + self.o_proj(attn2)
         prep = self.gate_up.prepare_input_rmsnorm(x2, self.post_norm, cfg.eps)
         gu = self.gate_up.apply_prepared(prep)
-        f = gu.shape[1] // 2
-        x2 = x2 + self.down(F.silu(gu[:, :f]) * gu[:, f:])
+        if self.fused_glue:
+            x2 = x2 + self.down.apply_prepared_reduced(self.down.local.prepare_input_swiglu(gu))
+        else:
+            f = gu.shape[1] // 2
+            x2 = x2 + self.down(F.silu(gu[:, :f]) * gu[:, f:])
         return x2.view(b, s, h)
 
 
@@ -158,16 +163,12 @@ class SharqDecoderLayer(torch.nn.Module):
         b, s, h = x.shape
         x2 = x.reshape(b * s, h)
         qkv = nv["qkv"].apply_prepared(nv["qkv"].prepare_input_rmsnorm(x2, self.input_norm, cfg.eps))
-        nq, nk = cfg.heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim
-        q = qkv[:, :nq].view(b, s, cfg.heads, cfg.head_dim).transpose(1, 2)
-        k = qkv[:, nq:nq + nk].view(b, s, cfg.kv_heads, cfg.head_dim).transpose(1, 2)
-        v = qkv[:, nq + nk:].view(b, s, cfg.kv_heads, cfg.head_dim).transpose(1, 2)
-        attn = F.scaled_dot_product_attention(apply_rope(q, cos, sin), apply_rope(k, cos, sin), v, is_causal=True,
-                                              enable_gqa=True)
+        nq = cfg.heads * cfg.head_dim
+        q, k, v = _split_heads(qkv, b, s, cfg.heads, cfg.kv_heads, cfg.head_dim, cos, sin, self.fused_glue)
+        attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
         x2 = x2 + nv["o"](attn.transpose(1, 2).reshape(b * s, nq))
         gu = nv["gate_up"].apply_prepared(nv["gate_up"].prepare_input_rmsnorm(x2, self.post_norm, cfg.eps))
-        f = gu.shape[1] // 2
-        x2 = x2 + nv["down"](F.silu(gu[:, :f]) * gu[:, f:])
+        x2 = x2 + nv["down"](_swiglu(gu, self.fused_glue))
         return x2.view(b, s, h)
 
     @torch.no_grad()
@@ -182,16 +183,44 @@ class SharqDecoderLayer(torch.nn.Module):
 
         x2 = x.reshape(b * s, h)
         qkv = F.linear(norm(x2, self.input_norm), r["qkv"], r["qkv_bias"])
-        nq, nk = cfg.heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim
-        q = qkv[:, :nq].view(b, s, cfg.heads, cfg.head_dim).transpose(1, 2)
-        k = qkv[:, nq:nq + nk].view(b, s, cfg.kv_heads, cfg.head_dim).transpose(1, 2)
-        v = qkv[:, nq + nk:].view(b, s, cfg.kv_heads, cfg.head_dim).transpose(1, 2)
-        attn = F.scaled_dot_product_attention(apply_rope(q, cos, sin), apply_rope(k, cos, sin), v, is_causal=True,
-                                              enable_gqa=True)
+        nq = cfg.heads * cfg.head_dim
+        glue = "gate_up" in r  # BF16 comparison mode; the accuracy reference of a SharQ layer stays pure ATen
+        q, k, v = _split_heads(qkv, b, s, cfg.heads, cfg.kv_heads, cfg.head_dim, cos, sin, glue)
+        attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
         x2 = x2 + F.linear(attn.transpose(1, 2).reshape(b * s, nq), r["o"])
         y = norm(x2, self.post_norm)
-        x2 = x2 + F.linear(F.silu(F.linear(y, r["gate"])) * F.linear(y, r["up"]), r["down"])
+        if glue:
+            hmid = _swiglu(F.linear(y, r["gate_up"]), True)
+        else:
+            hmid = F.silu(F.linear(y, r["gate"])) * F.linear(y, r["up"])
+        x2 = x2 + F.linear(hmid, r["down"])
         return x2.view(b, s, h)
+
+
+def _split_heads(qkv: torch.Tensor, b: int, s: int, heads: int, kv_heads: int, d: int, cos: torch.Tensor,
+                 sin: torch.Tensor, fused: bool):
+    """Merged qkv activation [b*s, (heads + 2*kv_heads)*d] -> rotated q, k and v as [b, H, s, d]
+    views.  fused: one in-place kernel on the q and k columns; else the ATen composition."""
+    nq, nk = heads * d, kv_heads * d
+    if fused and qkv.is_cuda:
+        from . import ops
+
+        ops.rope_inplace_(qkv, heads + kv_heads, d, cos, sin, s)
+    q = qkv[:, :nq].view(b, s, heads, d).transpose(1, 2)
+    k = qkv[:, nq:nq + nk].view(b, s, kv_heads, d).transpose(1, 2)
+    v = qkv[:, nq + nk:].view(b, s, kv_heads, d).transpose(1, 2)
+    if not (fused and qkv.is_cuda):
+        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+    return q, k, v
+
+
+def _swiglu(gu: torch.Tensor, fused: bool) -> torch.Tensor:
+    if fused and gu.is_cuda:
+        from . import ops
+
+        return ops.swiglu(gu.contiguous())
+    f = gu.shape[1] // 2
+    return F.silu(gu[:, :f]) * gu[:, f:]
 
 
 def _local_column(w_local: torch.Tensor, w_full: torch.Tensor, bias):
@@ -209,12 +238,13 @@ class SharqDecoder(torch.nn.Module):
     """Embedding -> N decoder layers -> final norm -> (bf16) lm_head on the last token."""
 
     def __init__(self, cfg: DecoderConfig, device, world: int = 1, rank: int = 0, seed: int = 0,
-                 keep_reference: bool = False, mode: str = "SHARQ"):
+                 keep_reference: bool = False, mode: str = "SHARQ", fused_glue: bool = True):
         super().__init__()
         self.cfg = cfg
         gen = torch.Generator(device=device).manual_seed(seed)
         self.embed = (0.02 * torch.randn(cfg.vocab, cfg.hidden, generator=gen, device=device)).to(torch.bfloat16)
-        self.layers = torch.nn.ModuleList([SharqDecoderLayer(cfg, gen, device, world, rank, keep_reference, mode) for _ in range(cfg.layers)])
+        self.layers = torch.nn.ModuleList([SharqDecoderLayer(cfg, gen, device, world, rank, keep_reference, mode, fused_glue)
+                                           for _ in range(cfg.layers)])
         self.final_norm = (1 + 0.1 * torch.randn(cfg.hidden, generator=gen, device=device)).to(torch.bfloat16)
         self.lm_head = (0.02 * torch.randn(cfg.vocab, cfg.hidden, generator=gen, device=device)).to(torch.bfloat16)
 

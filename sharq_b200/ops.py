@@ -192,6 +192,60 @@ def fused_rmsnorm_sparse_residual_quantize_x(X: torch.Tensor, rmsnorm_weight: to
     return _scaled_prepare(X, w, rmsnorm_eps, N, return_workspace)
 
 
+def rope_inplace_(qkv: torch.Tensor, heads: int, head_dim: int, cos: torch.Tensor, sin: torch.Tensor,
+                  seq_len: int) -> torch.Tensor:
+    """Rotary embedding in place on the first `heads` heads of every row of qkv [rows, width]
+    (bf16, unit column stride); cos/sin bf16 [seq_len, head_dim]; position = row % seq_len.
+    Equals `x * cos + rotate_half(x) * sin` of the ATen ops, head by head."""
+    _check(qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.dim() == 2 and qkv.stride(1) == 1,
+           "qkv must be a CUDA bfloat16 matrix with unit column stride")
+    for t, name in ((cos, "cos"), (sin, "sin")):
+        _check(t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous() and tuple(t.shape) == (seq_len, head_dim),
+               f"{name} must be a contiguous CUDA bfloat16 tensor shaped [seq_len, head_dim]")
+    _check(heads * head_dim <= qkv.shape[1], "heads * head_dim exceeds the row width")
+    dev = qkv.device
+    with _on_device(dev):
+        _lib.check(_lib.lib().sharq_rope_inplace(_ptr(qkv), int(qkv.shape[0]), int(qkv.stride(0)), int(seq_len), int(heads),
+                                                 int(head_dim), _ptr(cos), _ptr(sin), _stream(dev)))
+    return qkv
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up of a contiguous bf16 [M, 2F] activation (gate columns first) -> bf16 [M, F]."""
+    _check(gate_up.is_cuda and gate_up.dtype == torch.bfloat16 and gate_up.dim() == 2 and gate_up.is_contiguous(),
+           "gate_up must be a contiguous CUDA bfloat16 matrix")
+    M, F2 = int(gate_up.shape[0]), int(gate_up.shape[1])
+    _check(F2 % 16 == 0, f"gate_up width must be a multiple of 16, got {F2}")
+    H = torch.empty((M, F2 // 2), dtype=torch.bfloat16, device=gate_up.device)
+    with _on_device(gate_up.device):
+        _lib.check(_lib.lib().sharq_swiglu(_ptr(gate_up), M, F2 // 2, _ptr(H), _stream(gate_up.device)))
+    return H
+
+
+def swiglu_sparse_residual_quantize_x(gate_up: torch.Tensor, N: int):
+    """silu(gate) * up followed by the scaled prepare of the product, for down_proj:
+    -> (A_comp, E, SFA_sparse, Q_res, SF_res, scale).  Equals
+    scaled_sparse_residual_quantize_x(swiglu(gate_up), N) in two launches: the SwiGLU kernel
+    also produces the tensor absmax, so the prepare needs no statistics pass."""
+    _check(gate_up.is_cuda and gate_up.dtype == torch.bfloat16 and gate_up.dim() == 2 and gate_up.is_contiguous(),
+           "gate_up must be a contiguous CUDA bfloat16 matrix")
+    M, F2 = int(gate_up.shape[0]), int(gate_up.shape[1])
+    K = F2 // 2
+    _check(F2 % 2 == 0 and K % 128 == 0, f"swiglu_sparse_residual_quantize_x requires K to be a multiple of 128, got {K}")
+    dev = gate_up.device
+    ws_bytes = 256
+    h_bytes = M * K * 2
+    A_comp, E, SFA, Q_res, SF_res, tail = _prepare_buffers(M, K, dev, extra=512 + h_bytes)
+    ws = tail[:ws_bytes]
+    scale = tail[256:260].view(torch.float32).reshape(())
+    H = tail[512:512 + h_bytes]
+    with _on_device(dev):
+        _lib.check(_lib.lib().sharq_swiglu_sparse_residual_quantize_x(
+            _ptr(gate_up), M, int(N), K, _ptr(H), _ptr(ws), ws_bytes, _ptr(A_comp), _ptr(E), _ptr(SFA), _ptr(Q_res),
+            _ptr(SF_res), _ptr(scale), _stream(dev)))
+    return A_comp, E, SFA, Q_res, SF_res, scale
+
+
 def scaled_sparse_residual_quantize_x(X: torch.Tensor, N: int):
     """Unscaled bf16 X -> (A_comp, E, SFA_sparse, Q_res, SF_res, scale): tensor scale,
     division and prepare in two launches (extra op, not in the reference)."""

@@ -107,6 +107,17 @@ class QLinearLayer(nn.Module):
         return self.prepare_input(x_norm, out_features_hint=out_features_hint)
 
     @torch.no_grad()
+    def prepare_input_swiglu(self, gate_up_2d: torch.Tensor, out_features_hint: Optional[int] = None):
+        """Prepared activation of act_fn(gate) * up for this (down_proj) layer from the merged
+        gate_up output [M, 2 * in_features]: the three ATen passes of
+        model/qLlamaLayer.py:183-185 and the activation quantisation in two launches."""
+        if self.quant_type != "SHARQ":
+            return self.prepare_input(ops.swiglu(gate_up_2d.to(torch.bfloat16)), out_features_hint)
+        n = self.out_features if out_features_hint is None else int(out_features_hint)
+        a_comp, e, sfa, q_res, sf_res, scale_x = ops.swiglu_sparse_residual_quantize_x(gate_up_2d, n)
+        return ("SHARQ", a_comp, e, sfa, q_res, sf_res, scale_x)
+
+    @torch.no_grad()
     def apply_prepared(self, prepared, out=None):
         """out: optional bf16 [M, N] tensor the fused SharQ GEMM writes into (used by the
         tensor-parallel layers to place partial sums in symmetric memory)."""
