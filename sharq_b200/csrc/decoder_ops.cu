@@ -25,6 +25,18 @@ __device__ __forceinline__ float hi_f(uint32_t w) { return __uint_as_float(w & 0
 
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
+__device__ __forceinline__ float exp2f_approx(float v) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+
+__device__ __forceinline__ float rcp_approx(float v) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t *>(&v);
@@ -76,32 +88,61 @@ __global__ void __launch_bounds__(256) rope_kernel(__nv_bfloat16 *__restrict__ x
   }
 }
 
-// silu as ATen computes it for a bf16 tensor: x / (1 + exp(-x)) in float, rounded to bf16
-__device__ __forceinline__ float silu_bf16(float x) { return round_bf16(x / (1.0f + expf(-x))); }
+// silu as ATen computes it for a bf16 tensor: x / (1 + exp(-x)) in float, rounded to bf16.
+// The kernel would be bound by the accurate expf and the IEEE division, so the value is first
+// formed with the approximate exp2 and reciprocal units: for |x| <= 16 that result is within
+// (1.5 |x| + 8) * 2^-24 <= 2^-19 relative (32 float ulps) of the true value (argument
+// rounding 1.5 |x|, ex2.approx 4, the addition 1, rcp.approx 2, the product 1), and the
+// accurate formula within 3 ulps.  When the fast value lies more than 40 ulps from every bf16
+// rounding boundary (float bits ...8000) both round to the same bf16 number; otherwise, and
+// for |x| > 16, the accurate formula is evaluated.
+__device__ __forceinline__ float silu_accurate(float x) { return x / (1.0f + expf(-x)); }
+
+__device__ __forceinline__ float silu_bf16(float x) {
+  const float e = exp2f_approx(-1.4426950408889634f * x);
+  const float fast = x * rcp_approx(1.0f + e);
+  const uint32_t t = (__float_as_uint(fast) + 0x8000u + 40u) & 0xFFFFu;
+  float v = fast;
+  if (!(fabsf(x) <= 16.0f && t >= 81u)) v = silu_accurate(x);
+  return round_bf16(v);
+}
 
 __global__ void __launch_bounds__(256) swiglu_absmax_kernel(const __nv_bfloat16 *__restrict__ gate_up, long long rows,
                                                             int ffn, long long row_stride, __nv_bfloat16 *__restrict__ h,
                                                             unsigned int *__restrict__ amax_bits) {
   __shared__ float warp_max[8];
   const int vecs = ffn >> 3;
-  const long long total = rows * vecs;
   float mx = 0.0f;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const long long row = i / vecs;
-    const int v = (int)(i % vecs);
-    const __nv_bfloat16 *g = gate_up + row * row_stride + v * 8;
-    const uint4 g4 = __ldg(reinterpret_cast<const uint4 *>(g));
-    const uint4 u4 = __ldg(reinterpret_cast<const uint4 *>(g + ffn));
-    const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w};
-    uint32_t o[4];
+  // a CTA walks rows, its threads the 16-byte vectors of a row, two vectors in flight per thread
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const __nv_bfloat16 *grow = gate_up + row * row_stride;
+    __nv_bfloat16 *hrow = h + row * (long long)ffn;
+    for (int v0 = threadIdx.x; v0 < vecs; v0 += 2 * blockDim.x) {
+      uint4 g4[2], u4[2];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float a = round_bf16(__fmul_rn(silu_bf16(lo_f(gw[j])), lo_f(uw[j])));
-      const float b = round_bf16(__fmul_rn(silu_bf16(hi_f(gw[j])), hi_f(uw[j])));
-      mx = fmaxf(mx, fmaxf(fabsf(a), fabsf(b)));
-      o[j] = pack2(a, b);
+      for (int t = 0; t < 2; ++t) {
+        const int v = v0 + t * blockDim.x;
+        if (v < vecs) {
+          g4[t] = __ldg(reinterpret_cast<const uint4 *>(grow + v * 8));
+          u4[t] = __ldg(reinterpret_cast<const uint4 *>(grow + ffn + v * 8));
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const int v = v0 + t * blockDim.x;
+        if (v >= vecs) break;
+        const uint32_t gw[4] = {g4[t].x, g4[t].y, g4[t].z, g4[t].w}, uw[4] = {u4[t].x, u4[t].y, u4[t].z, u4[t].w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float a = round_bf16(__fmul_rn(silu_bf16(lo_f(gw[j])), lo_f(uw[j])));
+          const float b = round_bf16(__fmul_rn(silu_bf16(hi_f(gw[j])), hi_f(uw[j])));
+          mx = fmaxf(mx, fmaxf(fabsf(a), fabsf(b)));
+          o[j] = pack2(a, b);
+        }
+        *reinterpret_cast<uint4 *>(hrow + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
     }
-    *reinterpret_cast<uint4 *>(h + row * (long long)ffn + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
   }
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
@@ -150,8 +191,9 @@ cudaError_t run_swiglu_absmax(const void *gate_up, long long rows, int ffn, long
     cudaError_t err = cudaMemsetAsync(amax_bits, 0, sizeof(unsigned int), stream);
     if (err != cudaSuccess) return err;
   }
-  const long long items = rows * (ffn / 8);
-  swiglu_absmax_kernel<<<grid_for(items), 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(gate_up), rows, ffn,
+  long long ctas = (long long)sm_count() * 8;
+  if (ctas > rows) ctas = rows;
+  swiglu_absmax_kernel<<<(unsigned)ctas, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(gate_up), rows, ffn,
                                                             row_stride, static_cast<__nv_bfloat16 *>(h), amax_bits);
   return cudaGetLastError();
 }
