@@ -67,6 +67,17 @@ int sharq_fused_rmsnorm_sparse_residual_quantize_x(const void *x_bf16, const voi
                                                    size_t workspace_bytes, void *a_comp, void *e, void *sfa_sparse,
                                                    void *q_res, void *sf_res, float *scale_out, void *stream);
 
+/* The same with the decoder's residual add folded in (no counterpart in the reference, whose
+ * layer wrapper adds with ATen before the call, model/qLlamaLayer.py:216-221): the input is
+ * S = bf16(X + residual), rounded like the ATen add; the statistics kernel forms S, writes it
+ * to sum_out [M,K] (may alias neither input) and the prepare reads it.  Outputs equal
+ * sharq_fused_rmsnorm_sparse_residual_quantize_x(S, ...). */
+int sharq_fused_add_rmsnorm_sparse_residual_quantize_x(const void *x_bf16, const void *residual_bf16, void *sum_out_bf16,
+                                                       const void *rmsnorm_weight_bf16, float rmsnorm_eps, int m, int n,
+                                                       int k, void *workspace, size_t workspace_bytes, void *a_comp,
+                                                       void *e, void *sfa_sparse, void *q_res, void *sf_res,
+                                                       float *scale_out, void *stream);
+
 /* The non-RMSNorm activation path with its host-side passes folded in: computes
  * scale = clamp(max|X|/2688, 1e-9), X' = bf16(X/scale) and the prepare of X'.  Equals
  * global_nvfp4_scale + divide + fused_sparse_residual_quantize_x of the reference

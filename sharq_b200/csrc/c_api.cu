@@ -106,6 +106,23 @@ int sharq_fused_rmsnorm_sparse_residual_quantize_x(const void *x, const void *ga
                     "fused_rmsnorm_sparse_residual_quantize_x");
 }
 
+int sharq_fused_add_rmsnorm_sparse_residual_quantize_x(const void *x, const void *residual, void *sum_out,
+                                                       const void *gamma, float eps, int m, int n, int k, void *workspace,
+                                                       size_t workspace_bytes, void *a_comp, void *e, void *sfa_sparse,
+                                                       void *q_res, void *sf_res, float *scale_out, void *stream) {
+  (void)n;
+  SHARQ_REQUIRE(m > 0 && k > 0, "X must be shaped [M, K]");
+  SHARQ_REQUIRE(k % 128 == 0,
+                "fused_add_rmsnorm_sparse_residual_quantize_x requires K to be a multiple of 128, got %d", k);
+  SHARQ_REQUIRE(k / 32 <= 1024, "fused_add_rmsnorm_sparse_residual_quantize_x requires K/32 <= 1024, got %d", k / 32);
+  SHARQ_REQUIRE(x && residual && sum_out && gamma && a_comp && e && sfa_sparse && q_res && sf_res, "null buffer");
+  SHARQ_REQUIRE(workspace && workspace_bytes >= sharq::prepare_workspace_bytes(m), "workspace too small: need %zu bytes",
+                sharq::prepare_workspace_bytes(m));
+  return check_cuda(sharq::run_scaled_prepare(x, gamma, eps, m, k, workspace, nullptr, a_comp, e, sfa_sparse, q_res,
+                                              sf_res, scale_out, as_stream(stream), false, residual, sum_out),
+                    "fused_add_rmsnorm_sparse_residual_quantize_x");
+}
+
 int sharq_scaled_sparse_residual_quantize_x(const void *x, int m, int n, int k, void *workspace, size_t workspace_bytes,
                                             void *a_comp, void *e, void *sfa_sparse, void *q_res, void *sf_res,
                                             float *scale_out, void *stream) {

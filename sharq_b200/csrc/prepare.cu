@@ -61,7 +61,12 @@ __device__ __forceinline__ void raise_amax(unsigned int *amax_bits, float mx) {
 //   right by one thread), and the tensor-wide max of |bf16(x * inv_rms * gamma)|.
 // Many rows are resident per SM, so the serial sums of different rows overlap.
 // ---------------------------------------------------------------------------
+// With kAdd the row is first formed as bf16(x + residual) (the decoder's residual add, rounded
+// like the ATen add), stored to sum_out, and the statistics are those of the sum.
+template <bool kAdd>
 __global__ void __launch_bounds__(1024, 2) rms_stats_kernel(const __nv_bfloat16 *__restrict__ x,
+                                                          const __nv_bfloat16 *__restrict__ residual,
+                                                          __nv_bfloat16 *__restrict__ sum_out,
                                                           const __nv_bfloat16 *__restrict__ gamma, float eps, int k,
                                                           float *__restrict__ inv_rms,
                                                           unsigned int *__restrict__ amax_bits) {
@@ -81,6 +86,19 @@ __global__ void __launch_bounds__(1024, 2) rms_stats_kernel(const __nv_bfloat16 
       w[4 * j + 1] = v.y;
       w[4 * j + 2] = v.z;
       w[4 * j + 3] = v.w;
+    }
+    if (kAdd) {
+      const uint4 *rsrc = reinterpret_cast<const uint4 *>(residual + (size_t)row * k + (size_t)g * 32);
+      uint4 *dst = reinterpret_cast<uint4 *>(sum_out + (size_t)row * k + (size_t)g * 32);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 r = __ldg(rsrc + j);
+        const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+          w[4 * j + t] = pack_bf16x2(__fadd_rn(lo_f(w[4 * j + t]), lo_f(rw[t])), __fadd_rn(hi_f(w[4 * j + t]), hi_f(rw[t])));
+        dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+      }
     }
     float s = 0.0f;
 #pragma unroll
@@ -352,10 +370,15 @@ __global__ void __launch_bounds__(kPrepareThreads, kPrepareCtasPerSm) prepare_ke
   const int aligned_m = (m + 127) / 128 * 128;
 
   __shared__ ScaleTables tbl;
+  extern __shared__ uint4 gamma_smem[];  // mode 1: the whole RMSNorm weight, k bf16
   if (threadIdx.x < 128) {
     const float v = ue4m3_to_float(threadIdx.x);
     tbl.value[threadIdx.x] = v;
     tbl.recip[threadIdx.x] = __frcp_rn(v);  // code 0 is never looked up (scales are clamped to >= 2^-9)
+  }
+  if (kMode == 1) {
+    const uint4 *gsrc = reinterpret_cast<const uint4 *>(p.gamma);
+    for (int i = threadIdx.x; i < k / 8; i += blockDim.x) gamma_smem[i] = __ldg(gsrc + i);
   }
   __syncthreads();
 
@@ -388,6 +411,7 @@ __global__ void __launch_bounds__(kPrepareThreads, kPrepareCtasPerSm) prepare_ke
   // persistent loop over 32-row x 256-column tiles; the next tile's 64 bytes are loaded
   // before the current tile is processed, so the loads overlap the arithmetic
   uint4 next[4];
+  float next_inv = 0.0f;
   auto issue_loads = [&](int tile) {
     const int row = (tile / k_tiles) * kRowsPerCta + row_in_tile;
     const int group = (tile % k_tiles) * kGroupsPerWarp + group_in_tile;
@@ -395,6 +419,7 @@ __global__ void __launch_bounds__(kPrepareThreads, kPrepareCtasPerSm) prepare_ke
       const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (size_t)row * k + (size_t)group * 32);
 #pragma unroll
       for (int j = 0; j < 4; ++j) next[j] = __ldg(src + j);
+      if (kMode == 1) next_inv = p.inv_rms[row];
     }
   };
   issue_loads(blockIdx.x);
@@ -414,6 +439,7 @@ __global__ void __launch_bounds__(kPrepareThreads, kPrepareCtasPerSm) prepare_ke
       xw[4 * j + 2] = next[j].z;
       xw[4 * j + 3] = next[j].w;
     }
+    const float inv = next_inv;
     issue_loads(tile + gridDim.x);
 
     GroupOut o;
@@ -426,11 +452,10 @@ __global__ void __launch_bounds__(kPrepareThreads, kPrepareCtasPerSm) prepare_ke
 
     if (live) {
       if (kMode == 1) {
-        const float inv = p.inv_rms[row];
-        const uint4 *gsrc = reinterpret_cast<const uint4 *>(p.gamma + (size_t)group * 32);
+        const uint4 *gsrc = gamma_smem + (size_t)group * 4;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          uint4 gv = __ldg(gsrc + j);
+          uint4 gv = gsrc[j];
           uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
 #pragma unroll
           for (int t = 0; t < 4; ++t) {
@@ -512,7 +537,15 @@ static cudaError_t launch_prepare(int mode, bool debug, const PrepareParams &p, 
   } else if (mode == 0) {
     prepare_kernel<0, false><<<grid, block, 0, stream>>>(p);
   } else if (mode == 1) {
-    prepare_kernel<1, false><<<grid, block, 0, stream>>>(p);
+    const size_t gamma_bytes = (size_t)p.k * sizeof(__nv_bfloat16);
+    static bool attr_set[64] = {};
+    int dev = 0;
+    if (gamma_bytes > 48 * 1024 && cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && !attr_set[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(prepare_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+      if (e != cudaSuccess) return e;
+      attr_set[dev] = true;
+    }
+    prepare_kernel<1, false><<<grid, block, gamma_bytes, stream>>>(p);
   } else {
     prepare_kernel<2, false><<<grid, block, 0, stream>>>(p);
   }
@@ -537,7 +570,9 @@ cudaError_t run_prepare(const void *x, int m, int k, void *a_comp, void *e, void
 
 cudaError_t run_scaled_prepare(const void *x, const void *gamma, float eps, int m, int k, void *workspace,
                                float *inv_rms_external, void *a_comp, void *e, void *sfa_sparse, void *q_res,
-                               void *sf_res, float *scale_out, cudaStream_t stream, bool absmax_ready) {
+                               void *sf_res, float *scale_out, cudaStream_t stream, bool absmax_ready,
+                               const void *residual, void *sum_out) {
+  if (residual != nullptr && (gamma == nullptr || sum_out == nullptr)) return cudaErrorInvalidValue;
   // workspace: [0,4) tensor absmax bits; [256, 256+4m) inv_rms
   auto *amax_bits = static_cast<unsigned int *>(workspace);
   float *inv_rms = inv_rms_external ? inv_rms_external
@@ -552,8 +587,16 @@ cudaError_t run_scaled_prepare(const void *x, const void *gamma, float eps, int 
   } else if (rms) {
     const int groups = k / 32;
     const int threads = (groups + 31) / 32 * 32;
-    rms_stats_kernel<<<m, threads, (size_t)groups * sizeof(float), stream>>>(
-        static_cast<const __nv_bfloat16 *>(x), static_cast<const __nv_bfloat16 *>(gamma), eps, k, inv_rms, amax_bits);
+    if (residual != nullptr) {
+      rms_stats_kernel<true><<<m, threads, (size_t)groups * sizeof(float), stream>>>(
+          static_cast<const __nv_bfloat16 *>(x), static_cast<const __nv_bfloat16 *>(residual),
+          static_cast<__nv_bfloat16 *>(sum_out), static_cast<const __nv_bfloat16 *>(gamma), eps, k, inv_rms, amax_bits);
+      x = sum_out;  // the prepare reads the sum
+    } else {
+      rms_stats_kernel<false><<<m, threads, (size_t)groups * sizeof(float), stream>>>(
+          static_cast<const __nv_bfloat16 *>(x), nullptr, nullptr, static_cast<const __nv_bfloat16 *>(gamma), eps, k,
+          inv_rms, amax_bits);
+    }
   } else {
     const size_t n16 = (size_t)m * k / 8;
     size_t blocks = (n16 + 255) / 256;

@@ -17,9 +17,11 @@ cudaError_t run_prepare(const void *x, int m, int k, void *a_comp, void *e, void
 // Row statistics + prepare with the tensor scale (and RMSNorm when gamma != nullptr)
 // applied inline.  inv_rms_external (optional) receives the per-row inv_rms instead of
 // the workspace slot.  With absmax_ready (gamma == nullptr only) the workspace already
-// holds the bits of max|x| and the statistics pass is skipped.
+// holds the bits of max|x| and the statistics pass is skipped.  With residual (RMSNorm path
+// only) the input is bf16(x + residual), which the statistics kernel also writes to sum_out.
 cudaError_t run_scaled_prepare(const void *x, const void *gamma, float eps, int m, int k, void *workspace,
                                float *inv_rms_external, void *a_comp, void *e, void *sfa_sparse, void *q_res,
-                               void *sf_res, float *scale_out, cudaStream_t stream, bool absmax_ready = false);
+                               void *sf_res, float *scale_out, cudaStream_t stream, bool absmax_ready = false,
+                               const void *residual = nullptr, void *sum_out = nullptr);
 
 }  // namespace sharq

@@ -132,30 +132,45 @@ class SharqDecoderLayer(torch.nn.Module):
         self.post_norm = (1 + 0.1 * torch.randn(h, generator=gen, device=device)).to(torch.bfloat16)
 
     @torch.no_grad()
-    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-        """x: [B, S, hidden] bf16 -> same shape."""
-        if self.mode == "BF16":
-            return self.forward_reference(x, cos, sin)
-        if self.mode == "NVFP4":
-            return self._forward_nvfp4(x, cos, sin)
+    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, delta: torch.Tensor = None,
+                return_delta: bool = False):
+        """x: [B, S, hidden] bf16 -> same shape.  delta: an addend of x that the caller has not
+        applied yet (the previous layer's down_proj output); with return_delta the layer returns
+        (x_mid, d) whose sum is its output, so that the next layer can fold the add into the
+        statistics pass of its first prepare."""
+        if self.mode != "SHARQ":
+            if delta is not None:
+                x = x + delta
+            y = self.forward_reference(x, cos, sin) if self.mode == "BF16" else self._forward_nvfp4(x, cos, sin)
+            return (y, None) if return_delta else y
         cfg = self.cfg
         b, s, h = x.shape
         x2 = x.reshape(b * s, h)
-        prep = self.qkv.prepare_input_rmsnorm(x2, self.input_norm, cfg.eps)
+        if delta is not None and self.fused_glue:
+            prep, x2 = self.qkv.prepare_input_add_rmsnorm(x2, delta.reshape(b * s, h), self.input_norm, cfg.eps)
+        else:
+            if delta is not None:
+                x2 = x2 + delta.reshape(b * s, h)
+            prep = self.qkv.prepare_input_rmsnorm(x2, self.input_norm, cfg.eps)
         qkv = self.qkv.apply_prepared(prep)
         q, k, v = _split_heads(qkv, b, s, self.local_heads, self.local_kv, cfg.head_dim, cos, sin, self.fused_glue)
         attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
         attn2 = attn.transpose(1, 2).reshape(b * s, self.local_heads * cfg.head_dim)
-        x2 = x2 + self.o_proj(attn2)
-        prep = self.gate_up.prepare_input_rmsnorm(x2, self.post_norm, cfg.eps)
+        o = self.o_proj(attn2)
+        if self.fused_glue:
+            prep, x2 = self.gate_up.prepare_input_add_rmsnorm(x2, o, self.post_norm, cfg.eps)
+        else:
+            x2 = x2 + o
+            prep = self.gate_up.prepare_input_rmsnorm(x2, self.post_norm, cfg.eps)
         gu = self.gate_up.apply_prepared(prep)
         if self.fused_glue:
-            x2 = x2 + self.down.apply_prepared_reduced(self.down.local.prepare_input_swiglu(gu))
+            d = self.down.apply_prepared_reduced(self.down.local.prepare_input_swiglu(gu))
         else:
             f = gu.shape[1] // 2
-            x2 = x2 + self.down(F.silu(gu[:, :f]) * gu[:, f:])
-        return x2.view(b, s, h)
-
+            d = self.down(F.silu(gu[:, :f]) * gu[:, f:])
+        if return_delta:
+            return x2.view(b, s, h), d.view(b, s, h)
+        return (x2 + d).view(b, s, h)
 
     @torch.no_grad()
     def _forward_nvfp4(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
@@ -255,8 +270,14 @@ class SharqDecoder(torch.nn.Module):
         b, s = token_ids.shape
         x = self.embed[token_ids]
         cos, sin = rope_tables(s, self.cfg.head_dim, self.cfg.rope_theta, x.device)
+        delta = None
         for layer in self.layers:
-            x = layer.forward_reference(x, cos, sin) if reference else layer(x, cos, sin)
+            if reference:
+                x = layer.forward_reference(x, cos, sin)
+            else:
+                x, delta = layer(x, cos, sin, delta=delta, return_delta=True)
+        if delta is not None:
+            x = x + delta
         last = x[:, -1, :].float()
         last = last * torch.rsqrt(last.pow(2).mean(-1, keepdim=True) + self.cfg.eps) * self.final_norm.float()
         return (last.to(torch.bfloat16) @ self.lm_head.T).float()

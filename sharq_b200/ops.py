@@ -150,7 +150,7 @@ def _on_device(dev):
     return torch.cuda.device(dev)
 
 
-def _scaled_prepare(X, gamma, eps, N, return_workspace):
+def _scaled_prepare(X, gamma, eps, N, return_workspace, residual=None):
     M, K = int(X.shape[0]), int(X.shape[1])
     dev = X.device
     ws_bytes = 256 + 4 * M
@@ -159,6 +159,13 @@ def _scaled_prepare(X, gamma, eps, N, return_workspace):
     scale = tail[_round256(ws_bytes):_round256(ws_bytes) + 4].view(torch.float32).reshape(())
     L = _lib.lib()
     with _on_device(dev):
+        if residual is not None:
+            total = torch.empty_like(X)
+            _lib.check(L.sharq_fused_add_rmsnorm_sparse_residual_quantize_x(
+                X.data_ptr(), residual.data_ptr(), total.data_ptr(), gamma.data_ptr(), float(eps), M, N, K, ws.data_ptr(),
+                ws_bytes, A_comp.data_ptr(), E.data_ptr(), SFA.data_ptr(), Q_res.data_ptr(), SF_res.data_ptr(),
+                scale.data_ptr(), _stream(dev)))
+            return A_comp, E, SFA, Q_res, SF_res, scale, total
         if gamma is not None:
             _lib.check(L.sharq_fused_rmsnorm_sparse_residual_quantize_x(
                 X.data_ptr(), gamma.data_ptr(), float(eps), M, N, K, ws.data_ptr(), ws_bytes, A_comp.data_ptr(),
@@ -190,6 +197,23 @@ def fused_rmsnorm_sparse_residual_quantize_x(X: torch.Tensor, rmsnorm_weight: to
            f"fused_rmsnorm_sparse_residual_quantize_x currently requires K to be a multiple of 128, got {K}")
     _check(K // 32 <= 1024, f"fused_rmsnorm_sparse_residual_quantize_x requires K/32 <= 1024, got {K // 32}")
     return _scaled_prepare(X, w, rmsnorm_eps, N, return_workspace)
+
+
+def fused_add_rmsnorm_sparse_residual_quantize_x(X: torch.Tensor, residual: torch.Tensor, rmsnorm_weight: torch.Tensor,
+                                                 rmsnorm_eps: float, N: int):
+    """-> (A_comp, E, SFA_sparse, Q_res, SF_res, scale, S) with S = X + residual (bf16, as the ATen
+    add rounds) and the first six the RMSNorm-fused prepare of S.  The add rides on the row
+    statistics pass, so S costs no extra read of X."""
+    M, K = _check_x(X)
+    _check(residual.is_cuda and residual.dtype == torch.bfloat16 and residual.is_contiguous()
+           and tuple(residual.shape) == (M, K) and residual.device == X.device,
+           "residual must be a contiguous CUDA bfloat16 tensor shaped like X on the same device")
+    w = rmsnorm_weight
+    _check(w.is_cuda and w.is_contiguous() and w.dtype == torch.bfloat16 and w.dim() == 1 and w.shape[0] == K
+           and w.device == X.device, "rmsnorm_weight must be a contiguous CUDA bfloat16 tensor shaped [K] on X's device")
+    _check(K % 128 == 0, f"fused_add_rmsnorm_sparse_residual_quantize_x requires K to be a multiple of 128, got {K}")
+    _check(K // 32 <= 1024, f"fused_add_rmsnorm_sparse_residual_quantize_x requires K/32 <= 1024, got {K // 32}")
+    return _scaled_prepare(X, w, rmsnorm_eps, N, False, residual=residual)
 
 
 def rope_inplace_(qkv: torch.Tensor, heads: int, head_dim: int, cos: torch.Tensor, sin: torch.Tensor,

@@ -107,6 +107,20 @@ class QLinearLayer(nn.Module):
         return self.prepare_input(x_norm, out_features_hint=out_features_hint)
 
     @torch.no_grad()
+    def prepare_input_add_rmsnorm(self, x_2d: torch.Tensor, residual_2d: torch.Tensor, rmsnorm_weight: torch.Tensor,
+                                  rmsnorm_eps: float, out_features_hint: Optional[int] = None):
+        """(prepared activation of rmsnorm(x + residual), x + residual): the residual add of the
+        decoder layer rides on the row statistics pass of the RMSNorm-fused prepare."""
+        if self.quant_type == "SHARQ" and self.extra_fusion and x_2d.is_cuda:
+            n = self.out_features if out_features_hint is None else int(out_features_hint)
+            a_comp, e, sfa, q_res, sf_res, scale_x, total = ops.fused_add_rmsnorm_sparse_residual_quantize_x(
+                x_2d.to(torch.bfloat16).contiguous(), residual_2d.to(torch.bfloat16).contiguous(), rmsnorm_weight,
+                rmsnorm_eps, n)
+            return ("SHARQ", a_comp, e, sfa, q_res, sf_res, scale_x), total
+        total = x_2d + residual_2d
+        return self.prepare_input_rmsnorm(total, rmsnorm_weight, rmsnorm_eps, out_features_hint), total
+
+    @torch.no_grad()
     def prepare_input_swiglu(self, gate_up_2d: torch.Tensor, out_features_hint: Optional[int] = None):
         """Prepared activation of act_fn(gate) * up for this (down_proj) layer from the merged
         gate_up output [M, 2 * in_features]: the three ATen passes of

@@ -73,3 +73,20 @@ def test_decoder_fused_glue_equals_aten_glue():
     plain = SharqDecoder(cfg, dev, seed=3, fused_glue=False).prefill(ids)
     ops.check_device_errors()
     assert torch.equal(fused, plain)
+
+
+@pytest.mark.parametrize("m,k", [(2048, 4096), (130, 512), (64, 14336)])
+def test_add_rmsnorm_prepare_equals_two_step(m, k):
+    """Residual add folded into the row statistics pass against the ATen add followed by the
+    RMSNorm-fused prepare: the sum and every prepared byte must be identical."""
+    from sharq_b200 import ops
+
+    x = H.config0_x(m, k, 11).cuda()
+    r = H.config0_x(m, k, 12).cuda()
+    gamma = H.config0_gamma(k, 3).cuda()
+    total = x + r
+    want = ops.fused_rmsnorm_sparse_residual_quantize_x(total, gamma, 1e-6, 4096)
+    got = ops.fused_add_rmsnorm_sparse_residual_quantize_x(x, r, gamma, 1e-6, 4096)
+    assert torch.equal(got[6], total)
+    for name, a, b in zip(("a_comp", "e", "sfa", "q_res", "sf_res", "scale"), got[:6], want):
+        assert torch.equal(a.reshape(-1), b.reshape(-1)), name
