@@ -520,6 +520,118 @@ def cpu_baseline(seconds: float = 12.0, m: int = 128):
             "sample": f"SHARQ_SIM layer (oracle/sharq_sim.py), M={m}, K=N=4096, {it} iterations, weights pre-quantised"}
 
 
+def run_shape_sweep(args):
+    """Config-1 sweep on one GPU: for M in {16, 128, 2048, 8192} and each Llama-3-8B projection
+    shape, device time of the activation prepare, the fused SharQ GEMM and the dense NVFP4 path
+    (dense quantisation + dense GEMM) on the same inputs, with roofline fractions.  Prints one
+    JSON line; not the headline metric."""
+    import torch
+
+    from sharq_b200 import ops
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the SharQ kernels have no CPU fallback")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = load_peaks()
+    p_dense = 4.0 * peaks["bf16_tflops_sustained"]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # larger than L2
+
+    def timed(fn, iters):
+        fn()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(iters):
+            flush.zero_()  # evict the operands between timed launches
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        return total / iters * 1e3  # us
+
+    def timed_rotating(make_call, copies):
+        """Small ops are launch-bound when timed one by one: capture the op on `copies` different
+        weight copies (together larger than L2, so every launch streams its weights from HBM) in
+        one CUDA graph, replay it, and return the time per launch in us."""
+        calls = [make_call(i) for i in range(copies)]
+        for c in calls:
+            c()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for c in calls:
+                c()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        g.reset()
+        return e0.elapsed_time(e1) / (3 * copies) * 1e3
+
+    cg = torch.Generator().manual_seed(0)
+    rows = []
+    for name, (n, k) in SHAPES.items():
+        w = (0.02 * torch.randn(n, k, generator=cg)).to(torch.bfloat16).to(dev)
+        w_scaled = (w.float() / (w.float().abs().max() / 2688.0)).to(torch.bfloat16)
+        qw, sfs, sfd = ops.quantize_w32_shared(w_scaled)
+        qw_d, sfw_d = ops.quantize_w_nvfp4(w_scaled)
+        gamma = (1 + 0.1 * torch.randn(k, generator=cg)).to(torch.bfloat16).to(dev) if k // 32 <= 1024 else None
+        del w, w_scaled
+        for m in (16, 128, 2048, 8192):
+            x = torch.randn(m, k, generator=cg)
+            x[:, torch.randperm(k, generator=cg)[: k // 100]] *= 20.0
+            x = x.to(torch.bfloat16).to(dev)
+            iters = 5 if m >= 2048 else 10
+            prep = ops.scaled_sparse_residual_quantize_x(x, n)
+            t_prep = timed(lambda: ops.scaled_sparse_residual_quantize_x(x, n), iters)
+            t_prep_rms = timed(lambda: ops.fused_rmsnorm_sparse_residual_quantize_x(x, gamma, 1e-6, n), iters) if gamma is not None else None
+            a_comp, e, sfa, q_res, sf_res, scale = prep
+            alpha = float(scale.item())
+            xs = (x.float() / scale).to(torch.bfloat16)
+            qx, sfx = ops.quantize_x_nvfp4(xs)
+            t_dq = timed(lambda: ops.quantize_x_nvfp4(xs), iters)
+            if m <= 128:
+                # weight-bound regime: rotate over weight copies inside one graph (see timed_rotating)
+                copies = max(2, int(300e6 // (n * k * 9 // 16)) + 1)
+                wq = [(qw.clone(), sfs.clone(), sfd.clone()) for _ in range(copies)]
+                t_gemm = timed_rotating(lambda i: (lambda: ops.sharq_linear_gemm(a_comp, e, sfa, q_res, sf_res, wq[i][0],
+                                                                                 wq[i][1], wq[i][2], alpha)), copies)
+                wd = [(qw_d.clone(), sfw_d.clone()) for _ in range(copies)]
+                t_dg = timed_rotating(lambda i: (lambda: ops.matmul(qx, wd[i][0], sfx, wd[i][1], alpha)), copies)
+                del wq, wd
+            else:
+                t_gemm = timed(lambda: ops.sharq_linear_gemm(a_comp, e, sfa, q_res, sf_res, qw, sfs, sfd, alpha), iters)
+                t_dg = timed(lambda: ops.matmul(qx, qw_d, sfx, sfw_d, alpha), iters)
+            ops.check_device_errors()
+            flops = 2.0 * m * n * k
+            weight_bytes = n * k / 2 + n * k / 16  # payload + 16-group scales, read once
+            rows.append({
+                "shape": name, "M": m, "N": n, "K": k,
+                "prepare_us": round(t_prep, 1), "prepare_rmsnorm_us": None if t_prep_rms is None else round(t_prep_rms, 1),
+                "prepare_hbm_frac": round(2.906 * m * k / (t_prep * 1e-6) / 1e9 / peaks["hbm_gbs"], 3),
+                "sharq_gemm_us": round(t_gemm, 1),
+                "sharq_gemm_dense_equiv_tflops": round(2 * flops / (t_gemm * 1e-6) / 1e12, 1),
+                "sharq_gemm_tensor_frac": round(1.5 * flops / (t_gemm * 1e-6) / 1e12 / p_dense, 3),
+                "sharq_gemm_weight_bw_frac": round(weight_bytes / (t_gemm * 1e-6) / 1e9 / peaks["hbm_gbs"], 3),
+                "nvfp4_quant_us": round(t_dq, 1), "nvfp4_gemm_us": round(t_dg, 1),
+                "nvfp4_gemm_tflops": round(flops / (t_dg * 1e-6) / 1e12, 1),
+                "sharq_linear_us": round(t_prep + t_gemm, 1), "nvfp4_linear_us": round(t_dq + t_dg, 1),
+            })
+            del x, xs, prep, a_comp, e, sfa, q_res, sf_res, qx, sfx
+        del qw, sfs, sfd, qw_d, sfw_d
+        torch.cuda.empty_cache()
+    print(json.dumps({"sweep": "config 1: SharQ GEMM shape sweep; M >= 2048: cold L2 (256 MB written between launches), "
+                               "M <= 128: GEMMs replayed from a CUDA graph over rotating weight copies larger than L2",
+                      "peaks": peaks, "tensor_frac_convention": "3*M*N*K dense-FP4-equivalent / (4 x bf16 sustained)",
+                      "rows": rows}), flush=True)
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -586,11 +698,15 @@ def main():
     ap.add_argument("--prefill-steps", type=int, default=3, help="0 skips the whole-model prefill measurement")
     ap.add_argument("--compare", action="store_true", help="also time the prefill with dense NVFP4 and bf16 linears (1 GPU)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph replay")
+    ap.add_argument("--shape-sweep", action="store_true",
+                    help="config-1 sweep (M in 16/128/2048/8192 x the four projection shapes) instead of the headline step")
     ap.add_argument("--kernel-table", action="store_true",
                     help="add per-kernel device time of one step (and of the prefill) to the JSON line")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.shape_sweep:
+        run_shape_sweep(args)
     else:
         run_ours(args)
 

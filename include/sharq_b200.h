@@ -154,6 +154,25 @@ int sharq_linear_gemm(const void *a_comp, const void *e, const void *sfa_sparse,
                       int k, float alpha, const float *alpha_dev, const void *bias_bf16, void *d, int *error_flag,
                       void *stream);
 
+/* The three GEMMs with caller-provided scratch (no counterpart in the reference).  With
+ * sharq_gemm_workspace_bytes(M, N) bytes (non-zero for M <= 128: M * N floats; contents
+ * need not be initialised) a small-M GEMM, which is bound by streaming the weights, splits K
+ * over the SMs: units add their fp32 partial sums into the scratch with vector reductions
+ * and a second kernel applies alpha / beta / bias and writes bf16.  The order of those fp32
+ * additions is not fixed, so the last bits of the sums may vary from call to call.  With
+ * workspace == NULL, or M > 128, these are the plain entry points. */
+size_t sharq_gemm_workspace_bytes(int m, int n);
+int sharq_matmul_ws(const void *a, const void *b, const void *sfa, const void *sfb, int m, int n, int k, float alpha,
+                    const float *alpha_dev, const void *c_in, float beta, void *d, void *workspace,
+                    size_t workspace_bytes, int *error_flag, void *stream);
+int sharq_sparse_matmul_ws(const void *a_comp, const void *b, const void *e, const void *sfa, const void *sfb, int m,
+                           int n, int k, float alpha, const float *alpha_dev, float beta, void *d, void *workspace,
+                           size_t workspace_bytes, int *error_flag, void *stream);
+int sharq_linear_gemm_ws(const void *a_comp, const void *e, const void *sfa_sparse, const void *q_res,
+                         const void *sf_res, const void *qw, const void *sfw_sparse, const void *sfw_dense, int m, int n,
+                         int k, float alpha, const float *alpha_dev, const void *bias_bf16, void *d, void *workspace,
+                         size_t workspace_bytes, int *error_flag, void *stream);
+
 /* No counterpart in the reference.  Same work and outputs as
  * sharq_fused_rmsnorm_sparse_residual_quantize_x, for callers that cannot allocate device
  * memory and have no spare buffer to pass as workspace (a server that has given all free

@@ -41,6 +41,12 @@ SIGNATURES = {
     "sharq_sparse_matmul": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_float, _P, c_float, _P, _P, _P]),
     "sharq_linear_gemm": (
         c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_float, _P, _P, _P, _P, _P]),
+    "sharq_gemm_workspace_bytes": (c_size_t, [c_int, c_int]),
+    "sharq_matmul_ws": (c_int, [_P, _P, _P, _P, c_int, c_int, c_int, c_float, _P, _P, c_float, _P, _P, c_size_t, _P, _P]),
+    "sharq_sparse_matmul_ws": (
+        c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_float, _P, c_float, _P, _P, c_size_t, _P, _P]),
+    "sharq_linear_gemm_ws": (
+        c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_float, _P, _P, _P, _P, c_size_t, _P, _P]),
     "sharq_set_gemm_tile_n": (c_int, [c_int]),
     "sharq_allreduce_bf16_multimem": (c_int, [_P, POINTER(c_void_p), c_int, c_int, c_size_t, c_int, _P, _P]),
     "sharq_allreduce_flag_bytes": (c_size_t, []),

@@ -228,8 +228,18 @@ int sharq_set_gemm_tile_n(int tile_n) {
   return 0;
 }
 
+size_t sharq_gemm_workspace_bytes(int m, int n) {
+  return (m > 0 && m <= 128 && n > 0) ? (size_t)m * (size_t)n * sizeof(float) : 0;
+}
+
 int sharq_matmul(const void *a, const void *b, const void *sfa, const void *sfb, int m, int n, int k, float alpha,
                  const float *alpha_dev, const void *c_in, float beta, void *d, int *error_flag, void *stream) {
+  return sharq_matmul_ws(a, b, sfa, sfb, m, n, k, alpha, alpha_dev, c_in, beta, d, nullptr, 0, error_flag, stream);
+}
+
+int sharq_matmul_ws(const void *a, const void *b, const void *sfa, const void *sfb, int m, int n, int k, float alpha,
+                    const float *alpha_dev, const void *c_in, float beta, void *d, void *workspace,
+                    size_t workspace_bytes, int *error_flag, void *stream) {
   SHARQ_REQUIRE(m > 0 && n > 0 && k > 0, "M, N, K must be positive");
   SHARQ_REQUIRE(k % 64 == 0, "matmul requires K to be a multiple of 64, got %d", k);
   SHARQ_REQUIRE(a && b && sfa && sfb && d && error_flag, "null buffer");
@@ -249,11 +259,19 @@ int sharq_matmul(const void *a, const void *b, const void *sfa, const void *sfb,
   g.k = k;
   g.tile_n = g_tile_n;
   g.error_flag = error_flag;
+  g.workspace = workspace;
+  g.workspace_bytes = workspace ? workspace_bytes : 0;
   return check_cuda(sharq::run_gemm(g, as_stream(stream)), "matmul");
 }
 
 int sharq_sparse_matmul(const void *a_comp, const void *b, const void *e, const void *sfa, const void *sfb, int m, int n,
                         int k, float alpha, const float *alpha_dev, float beta, void *d, int *error_flag, void *stream) {
+  return sharq_sparse_matmul_ws(a_comp, b, e, sfa, sfb, m, n, k, alpha, alpha_dev, beta, d, nullptr, 0, error_flag, stream);
+}
+
+int sharq_sparse_matmul_ws(const void *a_comp, const void *b, const void *e, const void *sfa, const void *sfb, int m, int n,
+                           int k, float alpha, const float *alpha_dev, float beta, void *d, void *workspace,
+                           size_t workspace_bytes, int *error_flag, void *stream) {
   SHARQ_REQUIRE(m > 0 && n > 0 && k > 0, "M, N, K must be positive");
   SHARQ_REQUIRE(beta == 0.0f, "sparse_matmul currently requires beta == 0");
   SHARQ_REQUIRE(k % 128 == 0, "sparse_matmul requires K to be a multiple of 128, got %d", k);
@@ -272,12 +290,22 @@ int sharq_sparse_matmul(const void *a_comp, const void *b, const void *e, const 
   g.k = k;
   g.tile_n = g_tile_n;
   g.error_flag = error_flag;
+  g.workspace = workspace;
+  g.workspace_bytes = workspace ? workspace_bytes : 0;
   return check_cuda(sharq::run_gemm(g, as_stream(stream)), "sparse_matmul");
 }
 
 int sharq_linear_gemm(const void *a_comp, const void *e, const void *sfa_sparse, const void *q_res, const void *sf_res,
                       const void *qw, const void *sfw_sparse, const void *sfw_dense, int m, int n, int k, float alpha,
                       const float *alpha_dev, const void *bias, void *d, int *error_flag, void *stream) {
+  return sharq_linear_gemm_ws(a_comp, e, sfa_sparse, q_res, sf_res, qw, sfw_sparse, sfw_dense, m, n, k, alpha, alpha_dev, bias,
+                              d, nullptr, 0, error_flag, stream);
+}
+
+int sharq_linear_gemm_ws(const void *a_comp, const void *e, const void *sfa_sparse, const void *q_res, const void *sf_res,
+                         const void *qw, const void *sfw_sparse, const void *sfw_dense, int m, int n, int k, float alpha,
+                         const float *alpha_dev, const void *bias, void *d, void *workspace, size_t workspace_bytes,
+                         int *error_flag, void *stream) {
   SHARQ_REQUIRE(m > 0 && n > 0 && k > 0, "M, N, K must be positive");
   SHARQ_REQUIRE(k % 128 == 0, "linear_gemm requires K to be a multiple of 128, got %d", k);
   SHARQ_REQUIRE(a_comp && e && sfa_sparse && q_res && sf_res && qw && sfw_sparse && sfw_dense && d && error_flag,
@@ -300,6 +328,8 @@ int sharq_linear_gemm(const void *a_comp, const void *e, const void *sfa_sparse,
   g.k = k;
   g.tile_n = g_tile_n;
   g.error_flag = error_flag;
+  g.workspace = workspace;
+  g.workspace_bytes = workspace ? workspace_bytes : 0;
   return check_cuda(sharq::run_gemm(g, as_stream(stream)), "linear_gemm");
 }
 

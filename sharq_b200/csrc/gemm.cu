@@ -107,6 +107,11 @@ struct GemmParams {
   float beta;
   int m, n, k;
   int *error_flag;
+  // Split K (small M): every output tile is computed by k_splits units, each over its share of
+  // the K stages; their fp32 partial sums are added into splitk_acc [m, n] (zero-filled by the
+  // launcher) with vector reductions and a second kernel applies the epilogue.
+  int k_splits;
+  float *splitk_acc;
 };
 
 // Epilogue of 32 accumulator columns held in registers: d = bf16(alpha * acc + beta * c_in),
@@ -192,7 +197,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   // work units: a unit is one output tile of a CTA (128 x BN) or of a pair (256 x BN)
   const int m_units = PAIR ? (p.m + 255) / 256 : (p.m + kBM - 1) / kBM;
   const int n_tiles = (p.n + BN - 1) / BN;
-  const int num_units = m_units * n_tiles;
+  const int k_splits = p.k_splits;
+  const int num_units = m_units * n_tiles * k_splits;
+  // unit -> (K share, tile); tiles M-fastest
+  auto k_begin = [&](int u) { return (int)((long long)k_stages * (u % k_splits) / k_splits); };
+  auto k_end = [&](int u) { return (int)((long long)k_stages * (u % k_splits + 1) / k_splits); };
   const int unit0 = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int unit_stride = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
@@ -226,10 +235,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       uint32_t g = 0;  // stages issued so far, across tiles
       bool ok = true;
       for (int u = unit0; u < num_units && ok; u += unit_stride) {
-        const int m_tile = PAIR ? 2 * (u % m_units) + (int)cta_rank : (u % m_units);
-        const int n_tile = u / m_units;
+        const int tile = u / k_splits;
+        const int m_tile = PAIR ? 2 * (tile % m_units) + (int)cta_rank : (tile % m_units);
+        const int n_tile = tile / m_units;
         const int w_row = n_tile * BN + (PAIR ? (int)cta_rank * (BN / 2) : 0);
-        for (int it = 0; it < k_stages; ++it, ++g) {
+        for (int it = k_begin(u), it_end = k_end(u); it < it_end; ++it, ++g) {
           const int s = (int)(g % S);
           const uint32_t ph = (g / S) & 1u;
           TIMING_T0();
@@ -280,7 +290,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         uint32_t g = 0;
         bool ok = true;
         for (int u = unit0; u < num_units && ok; u += unit_stride) {
-          for (int it = 0; it < k_stages; ++it, ++g) {
+          for (int it = k_begin(u), it_end = k_end(u); it < it_end; ++it, ++g) {
             const int s = (int)(g % S);
             if (!ptx::mbar_wait(full_bar + s, (g / S) & 1u, abort_flag)) {
               *abort_flag = 1;
@@ -311,7 +321,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
           ptx::tc_fence_after();
           uint32_t accumulate = 0;
-          for (int it = 0; it < k_stages; ++it, ++g) {
+          for (int it = k_begin(u), it_end = k_end(u); it < it_end; ++it, ++g) {
             const int s = (int)(g % S);
             const uint32_t ph = (g / S) & 1u;
             TIMING_T0();
@@ -410,8 +420,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const bool has_c = (p.c_in != nullptr) && (beta != 0.0f);
     uint32_t tile_iter = 0;
     for (int u = unit0; u < num_units; u += unit_stride, ++tile_iter) {
-      const int m_tile = PAIR ? 2 * (u % m_units) + (int)cta_rank : (u % m_units);
-      const int n_tile = u / m_units;
+      const int tile = u / k_splits;
+      const int m_tile = PAIR ? 2 * (tile % m_units) + (int)cta_rank : (tile % m_units);
+      const int n_tile = tile / m_units;
       bool ok = ptx::mbar_wait(acc_full_bar, tile_iter & 1u, abort_flag);
       if (!ok) {
         *abort_flag = 1;
@@ -437,6 +448,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       }
       const int row = m_tile * kBM + quad * 32 + lane;
       const int col_base = n_tile * BN + half * kColsPerEpiWarp;
+      if (k_splits > 1) {
+        // partial sums of this K share: fp32 vector reductions into the accumulation buffer
+        if (row < p.m) {
+          float *dst = p.splitk_acc + (size_t)row * p.n + col_base;
+          const bool vec = (p.n & 3) == 0;
+#pragma unroll
+          for (int i = 0; i < kColsPerEpiWarp; i += 4) {
+            if (vec && col_base + i + 4 <= p.n) {
+              ptx::red_add_v4_f32(dst + i, __uint_as_float(acc[i]), __uint_as_float(acc[i + 1]),
+                                  __uint_as_float(acc[i + 2]), __uint_as_float(acc[i + 3]));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (col_base + i + j < p.n) atomicAdd(dst + i + j, __uint_as_float(acc[i + j]));
+            }
+          }
+        }
+        continue;
+      }
 #pragma unroll
       for (int c = 0; c < kColsPerEpiWarp / 32; ++c)
         epilogue_chunk(p, &acc[32 * c], row, col_base + 32 * c, alpha, beta, has_c);
@@ -449,6 +479,34 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc<CG>(tmem_base, L::kTmemCols);
+  }
+}
+
+// Second kernel of a split-K GEMM: the epilogue on the accumulated fp32 sums, 32 columns per thread.
+__global__ void __launch_bounds__(256) splitk_finalize_kernel(const GemmParams p) {
+  const int chunks = (p.n + 31) / 32;
+  const long long total = (long long)p.m * chunks;
+  const float alpha = p.alpha_ptr ? p.alpha * (*p.alpha_ptr) : p.alpha;
+  const bool has_c = (p.c_in != nullptr) && (p.beta != 0.0f);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int row = (int)(i / chunks);
+    const int col0 = (int)(i % chunks) * 32;
+    const float *src = p.splitk_acc + (size_t)row * p.n + col0;
+    uint32_t acc[32];
+    if ((p.n & 3) == 0 && col0 + 32 <= p.n) {
+#pragma unroll
+      for (int v = 0; v < 8; ++v) {
+        const float4 t = __ldcg(reinterpret_cast<const float4 *>(src) + v);
+        acc[4 * v] = __float_as_uint(t.x);
+        acc[4 * v + 1] = __float_as_uint(t.y);
+        acc[4 * v + 2] = __float_as_uint(t.z);
+        acc[4 * v + 3] = __float_as_uint(t.w);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) acc[j] = col0 + j < p.n ? __float_as_uint(__ldcg(src + j)) : 0u;
+    }
+    epilogue_chunk(p, acc, row, col0, alpha, p.beta, has_c);
   }
 }
 
@@ -549,7 +607,26 @@ cudaError_t launch(const GemmArgs &a, cudaStream_t stream) {
   p.error_flag = a.error_flag;
   const int n_tiles = (a.n + BN - 1) / BN;
   const int m_units = PAIR ? (a.m + 255) / 256 : (a.m + kBM - 1) / kBM;
-  const int units = m_units * n_tiles;
+  int units = m_units * n_tiles;
+  // Split K when one row of tiles cannot fill the GPU (M <= 128 is weight-bandwidth-bound: the
+  // weights must stream through as many SMs as possible) and the caller gave scratch.
+  p.k_splits = 1;
+  p.splitk_acc = nullptr;
+  const int k_stages = (a.k + kBK - 1) / kBK;
+  if (!PAIR && m_units == 1 && a.workspace != nullptr && a.workspace_bytes >= (size_t)a.m * a.n * sizeof(float)) {
+    int splits = sms / units;
+    if (splits > k_stages / 2) splits = k_stages / 2;  // at least two K stages per unit
+    // the fp32 reductions cost M x N x splits atomics: measured worth it for M <= 64 (qkv
+    // 16.2 -> 13.3 us, down 39.9 -> 17.3 us at M = 16) and for long K (down at M = 128:
+    // 41.0 -> 22.9 us), not for M = 128 with K = 4096 (17.8 -> 19.0 us)
+    if (splits >= 2 && (a.m <= 64 || k_stages >= 32)) {
+      p.k_splits = splits;
+      p.splitk_acc = static_cast<float *>(a.workspace);
+      units *= splits;
+      e = cudaMemsetAsync(a.workspace, 0, (size_t)a.m * a.n * sizeof(float), stream);
+      if (e != cudaSuccess) return e;
+    }
+  }
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   if (PAIR) {
@@ -567,7 +644,13 @@ cudaError_t launch(const GemmArgs &a, cudaStream_t stream) {
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = L::kSmemBytes;
   cfg.stream = stream;
-  return cudaLaunchKernelEx(&cfg, kernel, tm_w, tm_ad, tm_ac, p);
+  e = cudaLaunchKernelEx(&cfg, kernel, tm_w, tm_ad, tm_ac, p);
+  if (e != cudaSuccess || p.k_splits == 1) return e;
+  const long long chunks = (long long)a.m * ((a.n + 31) / 32);
+  long long blocks = (chunks + 255) / 256;
+  if (blocks > 4LL * sms) blocks = 4LL * sms;
+  splitk_finalize_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p);
+  return cudaGetLastError();
 }
 
 }  // namespace

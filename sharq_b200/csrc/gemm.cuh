@@ -2,6 +2,8 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <cstddef>
+
 namespace sharq {
 
 struct GemmArgs {
@@ -26,6 +28,10 @@ struct GemmArgs {
   int m = 0, n = 0, k = 0;
   int tile_n = 0;             // 0 = choose, else 128 or 256
   int *error_flag = nullptr;  // device int, set non-zero when a bounded wait ran out
+  // Optional scratch of at least m * n * 4 bytes: lets a GEMM with M <= 128 split K over the SMs
+  // (fp32 partial sums are accumulated there, a second kernel applies the epilogue).
+  void *workspace = nullptr;
+  size_t workspace_bytes = 0;
 };
 
 cudaError_t run_gemm(const GemmArgs &args, cudaStream_t stream);

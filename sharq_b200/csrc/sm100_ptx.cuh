@@ -69,6 +69,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Four consecutive floats added to global memory without a return value (16-byte aligned).
+__device__ __forceinline__ void red_add_v4_f32(float *addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 // Bounded wait.  Returns false on timeout or when *abort_flag became non-zero.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;

@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import contextlib
 import ctypes
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -374,15 +375,24 @@ def _scale_ptr(scale: torch.Tensor, reference: torch.Tensor, name: str):
     return _ptr(scale)
 
 
+def _gemm_scratch(M: int, N: int, dev):
+    """Scratch that lets a small-M GEMM split K over the SMs: (tensor or None, bytes)."""
+    if M > 128 or os.environ.get("SHARQ_GEMM_SPLIT_K", "1") == "0":
+        return None, 0
+    nbytes = int(_lib.lib().sharq_gemm_workspace_bytes(M, N))
+    return (torch.empty(nbytes, dtype=torch.uint8, device=dev), nbytes) if nbytes else (None, 0)
+
+
 def _dense_gemm(A, B, SFA, SFB, alpha, alpha_t, C_in, beta):
     M, N, K = int(A.shape[0]), int(B.shape[0]), int(A.shape[1]) * 2
     dev = A.device
     D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    ws, ws_bytes = _gemm_scratch(M, N, dev)
     with _on_device(dev):
-        _lib.check(_lib.lib().sharq_matmul(
+        _lib.check(_lib.lib().sharq_matmul_ws(
             _ptr(A), _ptr(B), _ptr(SFA), _ptr(SFB), M, N, K, float(alpha),
             None if alpha_t is None else _scale_ptr(alpha_t, A, "scale"), _ptr(C_in), float(beta), _ptr(D),
-            _ptr(_error_flag(dev)), _stream(dev)))
+            _ptr(ws), ws_bytes, _ptr(_error_flag(dev)), _stream(dev)))
     return D
 
 
@@ -435,11 +445,12 @@ def _sparse_gemm(name, A_comp, B, E, SFA, SFB, M, N, K, alpha, alpha_t, beta):
     _check(B.shape[1] == K // 2, f"B.size(1) mismatch: expected {K // 2}, got {B.shape[1]}")
     dev = A_comp.device
     D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    ws, ws_bytes = _gemm_scratch(M, N, dev)
     with _on_device(dev):
-        _lib.check(_lib.lib().sharq_sparse_matmul(
+        _lib.check(_lib.lib().sharq_sparse_matmul_ws(
             _ptr(A_comp), _ptr(B), _ptr(E), _ptr(SFA), _ptr(SFB), M, N, K, float(alpha),
             None if alpha_t is None else _scale_ptr(alpha_t, A_comp, "alpha"), float(beta), _ptr(D),
-            _ptr(_error_flag(dev)), _stream(dev)))
+            _ptr(ws), ws_bytes, _ptr(_error_flag(dev)), _stream(dev)))
     return D
 
 
@@ -472,12 +483,13 @@ def sharq_linear_gemm(A_comp, E, SFA_sparse, Q_res, SF_res, QW, SFW_sparse, SFW_
                and tuple(out.shape) == (M, N), "out must be a contiguous CUDA bfloat16 tensor shaped [M, N]")
         D = out
     alpha_t = alpha if isinstance(alpha, torch.Tensor) else None
+    ws, ws_bytes = _gemm_scratch(M, N, dev)
     with _on_device(dev):
-        _lib.check(_lib.lib().sharq_linear_gemm(
+        _lib.check(_lib.lib().sharq_linear_gemm_ws(
             _ptr(A_comp), _ptr(E), _ptr(SFA_sparse), _ptr(Q_res), _ptr(SF_res), _ptr(QW), _ptr(SFW_sparse),
             _ptr(SFW_dense), M, N, K, float(alpha_host) if alpha_t is not None else float(alpha) * float(alpha_host),
             None if alpha_t is None else _scale_ptr(alpha_t, Q_res, "alpha"), _ptr(bias), _ptr(D),
-            _ptr(_error_flag(dev)), _stream(dev)))
+            _ptr(ws), ws_bytes, _ptr(_error_flag(dev)), _stream(dev)))
     return D
 
 

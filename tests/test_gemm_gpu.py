@@ -120,3 +120,34 @@ def test_gemm_argument_errors():
         ops.sparse_matmul(z(7), z(128, 128), z(2048), z(4096), z(4096), 128, 128, 256)
     with pytest.raises(RuntimeError, match="exactly one element"):
         ops.matmul_tensor_scale(z(128, 128), z(128, 128), z(4096), z(4096), torch.ones(2, device="cuda"))
+
+
+@pytest.mark.parametrize("m,n,k", [(16, 6144, 4096), (128, 4096, 14336), (100, 1000, 1024), (1, 4096, 4096)])
+def test_small_m_split_k_agrees_with_single_pass(m, n, k, monkeypatch):
+    """M <= 128 with caller scratch: K split over the SMs (fp32 vector reductions + a finalize
+    kernel with alpha / beta / bias) against the same GEMM computed in one pass per tile."""
+    from sharq_b200 import ops
+
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g)
+    x[:, torch.randperm(k, generator=g)[: k // 100]] *= 20
+    w = (0.02 * torch.randn(n, k, generator=g)).to(torch.bfloat16).cuda()
+    bias = (0.5 * torch.randn(n, generator=g)).to(torch.bfloat16).cuda()
+    qw, sfs, sfd = ops.quantize_w32_shared((w.float() / (w.float().abs().max() / 2688)).to(torch.bfloat16))
+    a_comp, e, sfa, q_res, sf_res, scale = ops.scaled_sparse_residual_quantize_x(x.to(torch.bfloat16).cuda(), n)
+    alpha = float(scale.item()) / 2688
+
+    def run():
+        y_sparse = ops.sparse_matmul(a_comp, qw, e, sfa, sfs, m, n, k, alpha=alpha)
+        return (ops.sharq_linear_gemm(a_comp, e, sfa, q_res, sf_res, qw, sfs, sfd, alpha, bias=bias), y_sparse,
+                ops.matmul_accum(q_res, qw, sf_res, sfd, alpha, y_sparse, 0.5))
+
+    monkeypatch.setenv("SHARQ_GEMM_SPLIT_K", "1")
+    split = run()
+    monkeypatch.setenv("SHARQ_GEMM_SPLIT_K", "0")
+    whole = run()
+    ops.check_device_errors()
+    for a, b in zip(split, whole):
+        assert torch.isfinite(a.float()).all()
+        rel = float((a.float() - b.float()).norm() / b.float().norm())
+        assert rel <= 2e-3, rel
