@@ -49,7 +49,18 @@ constexpr int kEpiWarps = 8;
 __device__ unsigned long long g_timing[8];
 #define TIMING_T0() long long t0_ = clock64()
 #define TIMING_ADD(slot) do { atomicAdd(&g_timing[slot], (unsigned long long)(clock64() - t0_)); t0_ = clock64(); } while (0)
+// wall-clock (ns) stamps of CTA 0's phases, overwritten by every launch
+__device__ unsigned long long g_stamps[16];
+__device__ __forceinline__ void timing_stamp(int slot) {
+  if (blockIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_stamps[slot] = t;
+  }
+}
+#define TIMING_STAMP(slot) timing_stamp(slot)
 #else
+#define TIMING_STAMP(slot) do {} while (0)
 #define TIMING_T0() do {} while (0)
 #define TIMING_ADD(slot) do {} while (0)
 #endif
@@ -78,7 +89,8 @@ struct StageLayout {
   static constexpr int kOffSfaD = kOffSfbSp + kSfbSpBytes;
   static constexpr int kOffSfbD = kOffSfaD + kSfaDBytes;
   static constexpr int kStageBytes = (kOffSfbD + kSfbDBytes + 1023) / 1024 * 1024;
-  static constexpr int kMaxSmem = 227 * 1024 - 2048;
+  static constexpr int kOutStageBytes = kEpiWarps * 32 * 64;  // per epilogue warp 32 rows x 32 bf16 for the tile store
+  static constexpr int kMaxSmem = 227 * 1024 - 2048 - kOutStageBytes;
   static constexpr int kStagesFit = kMaxSmem / kStageBytes;
   static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
   // tensor memory columns
@@ -90,7 +102,8 @@ struct StageLayout {
   static constexpr int kColSfbD = kColSfaD + 16;
   static constexpr int kColEnd = kColSfbD + 4 * (BN / 32);
   static constexpr int kTmemCols = kColEnd <= 256 ? 256 : 512;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
+  static constexpr int kSmemBytes =
+      kStages * kStageBytes + kOutStageBytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
 };
 
 struct GemmParams {
@@ -112,14 +125,21 @@ struct GemmParams {
   // launcher) with vector reductions and a second kernel applies the epilogue.
   int k_splits;
   float *splitk_acc;
+  int staged_store;  // output tiles are transposed through shared memory for coalesced stores (N % 8 == 0)
 };
 
 // Epilogue of 32 accumulator columns held in registers: d = bf16(alpha * acc + beta * c_in),
 // then (+ bias) in bf16; rows >= M and columns >= N are masked.  A thread owns one row and
 // stores 64 contiguous bytes.
+// With `stage` non-null the 64 bytes go to row `stage_row` of a 32-row x 64-byte shared-memory
+// tile instead, 16-byte chunk v at position v ^ ((row >> 1) & 3) (no bank conflicts on the way in
+// or out); the caller stores the tile and masks rows >= M and columns >= N; requires N % 8 == 0.
 __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32_t *acc, int row, int col0, float alpha,
-                                               float beta, bool has_c) {
-  if (row >= p.m || col0 >= p.n) return;
+                                               float beta, bool has_c, uint8_t *stage = nullptr, int stage_row = 0) {
+  if (stage == nullptr && (row >= p.m || col0 >= p.n)) return;
+  if (stage != nullptr && (row >= p.m || col0 >= p.n)) {
+    has_c = false;  // masked by the caller's store; C_in must not be read out of range
+  }
   const size_t off = (size_t)row * p.n + col0;
   const bool full = (col0 + 32 <= p.n) && ((p.n & 7) == 0);
 #pragma unroll
@@ -142,21 +162,41 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32
           if (col0 + 8 * v + i < p.n) f[i] = __fmaf_rn(beta, __bfloat162float(p.c_in[off + 8 * v + i]), f[i]);
       }
     }
+    // two values per conversion instruction (the scalar conversion unit is the slow pipe here)
     uint32_t o[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      uint32_t lo = float_to_bf16_bits(f[2 * i]), hi = float_to_bf16_bits(f[2 * i + 1]);
-      if (p.bias != nullptr) {
-        // bias is added to the bf16 result, as a separate bf16 add would
-        const int cc = col0 + 8 * v + 2 * i;
-        float b0 = cc < p.n ? __bfloat162float(p.bias[cc]) : 0.0f;
-        float b1 = cc + 1 < p.n ? __bfloat162float(p.bias[cc + 1]) : 0.0f;
-        lo = float_to_bf16_bits(bf16_bits_to_float(lo) + b0);
-        hi = float_to_bf16_bits(bf16_bits_to_float(hi) + b1);
-      }
-      o[i] = lo | (hi << 16);
+      __nv_bfloat162 pair = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      o[i] = *reinterpret_cast<uint32_t *>(&pair);
     }
-    if (full) {
+    if (p.bias != nullptr) {
+      // bias is added to the bf16 result, as a separate bf16 add would (a bf16 add rounds the
+      // exact sum once, which is what the fp32 add + rounding of two bf16 values gives)
+      if (full && (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) {
+        const uint4 bv = __ldg(reinterpret_cast<const uint4 *>(p.bias + col0 + 8 * v));
+        const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          __nv_bfloat162 sum = __hadd2(*reinterpret_cast<__nv_bfloat162 *>(&o[i]),
+                                       *reinterpret_cast<const __nv_bfloat162 *>(&bw[i]));
+          o[i] = *reinterpret_cast<uint32_t *>(&sum);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int cc = col0 + 8 * v + 2 * i;
+          const float b0 = cc < p.n ? __bfloat162float(p.bias[cc]) : 0.0f;
+          const float b1 = cc + 1 < p.n ? __bfloat162float(p.bias[cc + 1]) : 0.0f;
+          const uint32_t lo = float_to_bf16_bits(bf16_bits_to_float(o[i] & 0xFFFFu) + b0);
+          const uint32_t hi = float_to_bf16_bits(bf16_bits_to_float(o[i] >> 16) + b1);
+          o[i] = lo | (hi << 16);
+        }
+      }
+    }
+    if (stage != nullptr) {
+      *reinterpret_cast<uint4 *>(stage + stage_row * 64 + ((v ^ ((stage_row >> 1) & 3)) << 4)) =
+          make_uint4(o[0], o[1], o[2], o[3]);
+    } else if (full) {
       *reinterpret_cast<uint4 *>(p.d + off + 8 * v) = make_uint4(o[0], o[1], o[2], o[3]);
     } else {
 #pragma unroll
@@ -206,6 +246,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const int unit_stride = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   if (threadIdx.x == 0) {
+    TIMING_STAMP(0);
     for (int s = 0; s < S; ++s) {
       ptx::mbar_init(full_bar + s, 1);
       ptx::mbar_init(empty_bar + s, 1);
@@ -225,6 +266,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (PAIR) ptx::cluster_sync();  // both CTAs' barriers exist before any remote arrive
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) TIMING_STAMP(1);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -280,6 +322,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                                 (uint32_t)n_sp * 512, full_bar + s);
           }
           TIMING_ADD(1);
+          if (g == 0) TIMING_STAMP(2);
         }
       }
     }
@@ -336,6 +379,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               break;
             }
             ptx::tc_fence_after();
+            if (g == 0) TIMING_STAMP(3);
             const uint32_t st = ptx::smem_u32(smem + s * L::kStageBytes);
             const int n_sp = SPARSE ? min(2, tiles_sp - 2 * it) : 0;
             const int n_d = DENSE ? min(4, tiles_d - 4 * it) : 0;
@@ -406,6 +450,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               ptx::tc_commit_multicast2(acc_full_bar, 3);
             else
               ptx::tc_commit<1>(acc_full_bar);
+            TIMING_STAMP(4);
           }
         }
       }
@@ -418,6 +463,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const float alpha = p.alpha_ptr ? p.alpha * (*p.alpha_ptr) : p.alpha;
     const float beta = p.beta;
     const bool has_c = (p.c_in != nullptr) && (beta != 0.0f);
+    // Output path: a lane holds one row of the accumulator, so a direct store instruction would
+    // touch 32 different rows with 16 bytes each (32 memory lines per instruction).  Every
+    // epilogue warp owns a 32-row x 64-byte shared-memory tile instead: 32 columns at a time are
+    // converted into it (swizzled, conflict-free), read back with four lanes per row, and
+    // stored as 8 rows x 64 contiguous bytes per instruction.
+    uint8_t *stage = p.staged_store ? smem + S * L::kStageBytes + 512 + ew * 2048 : nullptr;
     uint32_t tile_iter = 0;
     for (int u = unit0; u < num_units; u += unit_stride, ++tile_iter) {
       const int tile = u / k_splits;
@@ -431,12 +482,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after();
+      if (warp == 2 && lane == 0) TIMING_STAMP(5);
       uint32_t acc[kColsPerEpiWarp];
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(L::kColAcc + half * kColsPerEpiWarp);
 #pragma unroll
       for (int c = 0; c < kColsPerEpiWarp / 32; ++c)
         ptx::tmem_ld_32x32b_x32(taddr + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&acc[32 * c]));
       ptx::tmem_ld_wait();
+      if (warp == 2 && lane == 0) TIMING_STAMP(8);
       // the accumulator is in registers: give tensor memory back before the slow part
       ptx::tc_fence_before();
       __syncwarp();
@@ -467,9 +520,30 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         continue;
       }
+      if (stage != nullptr) {
+        const int row0 = m_tile * kBM + quad * 32;
 #pragma unroll
-      for (int c = 0; c < kColsPerEpiWarp / 32; ++c)
-        epilogue_chunk(p, &acc[32 * c], row, col_base + 32 * c, alpha, beta, has_c);
+        for (int c = 0; c < kColsPerEpiWarp / 32; ++c) {
+          const int col0 = col_base + 32 * c;
+          epilogue_chunk(p, &acc[32 * c], row, col0, alpha, beta, has_c, stage, lane);
+          __syncwarp();
+          const int gcol = col0 + (lane & 3) * 8;
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int r = it * 8 + (lane >> 2);
+            const uint4 v = *reinterpret_cast<const uint4 *>(stage + r * 64 + (((lane & 3) ^ ((r >> 1) & 3)) << 4));
+            if (row0 + r < p.m && gcol < p.n)
+              *reinterpret_cast<uint4 *>(p.d + (size_t)(row0 + r) * p.n + gcol) = v;
+          }
+          __syncwarp();
+          if (warp == 2 && lane == 0) TIMING_STAMP(9 + c);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < kColsPerEpiWarp / 32; ++c)
+          epilogue_chunk(p, &acc[32 * c], row, col_base + 32 * c, alpha, beta, has_c);
+      }
+      if (warp == 2 && lane == 0) TIMING_STAMP(6);
     }
   }
 
@@ -480,6 +554,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     ptx::tc_fence_after();
     ptx::tmem_dealloc<CG>(tmem_base, L::kTmemCols);
   }
+  if (threadIdx.x == 0) TIMING_STAMP(7);
 }
 
 // Second kernel of a split-K GEMM: the epilogue on the accumulated fp32 sums, 32 columns per thread.
@@ -590,6 +665,7 @@ cudaError_t launch(const GemmArgs &a, cudaStream_t stream) {
   if (SPARSE && !make_tmap_bytes(&tm_ac, a.a_comp, (uint64_t)a.m, (uint64_t)a.k / 4, kBM, 64, CU_TENSOR_MAP_SWIZZLE_64B))
     return cudaErrorInvalidValue;
   GemmParams p{};
+  p.staged_store = (a.n % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.d) & 15) == 0);
   p.e = static_cast<const uint8_t *>(a.e);
   p.sfa_sparse = static_cast<const uint8_t *>(a.sfa_sparse);
   p.sfa_dense = static_cast<const uint8_t *>(a.sfa_dense);
@@ -656,6 +732,10 @@ cudaError_t launch(const GemmArgs &a, cudaStream_t stream) {
 }  // namespace
 
 #ifdef SHARQ_GEMM_TIMING
+extern "C" int sharq_debug_read_stamps(unsigned long long *out) {
+  return cudaMemcpyFromSymbol(out, g_stamps, sizeof(g_stamps)) == cudaSuccess ? 0 : 1;
+}
+
 extern "C" int sharq_debug_read_timing(unsigned long long *out, int reset) {
   if (cudaMemcpyFromSymbol(out, g_timing, sizeof(g_timing)) != cudaSuccess) return 1;
   if (reset) {
