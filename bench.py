@@ -389,14 +389,18 @@ def run_ours(args):
         layers.clear()
         graph_keep = graph  # the captured step stays alive until teardown
         torch.cuda.empty_cache()
-        model = SharqDecoder(DecoderConfig.llama3_8b(layers=layers_n), dev, world=world, rank=rank, seed=7)
-        ids = torch.randint(0, model.cfg.vocab, (1, m), generator=torch.Generator().manual_seed(0)).to(dev)
+        make_cfg = getattr(DecoderConfig, args.prefill_model)
+        pcfg = make_cfg(layers=layers_n if args.prefill_model == "llama3_8b" else min(layers_n, make_cfg().layers))
+        p_batch, p_seq = args.prefill_batch, (m if args.prefill_seq <= 0 else args.prefill_seq)
+        model = SharqDecoder(pcfg, dev, world=world, rank=rank, seed=7)
+        ids = torch.randint(0, model.cfg.vocab, (p_batch, p_seq), generator=torch.Generator().manual_seed(0)).to(dev)
         for _ in range(2):
             logits = model.prefill(ids)
         barrier()
         ops.check_device_errors()
         pg = None
-        if not args.no_graph:
+        # the expert loop of a mixture-of-experts layer has data-dependent shapes: eager only
+        if not args.no_graph and pcfg.experts == 0:
             pg = torch.cuda.CUDAGraph()
             with torch.cuda.graph(pg):
                 logits = model.prefill(ids)
@@ -408,15 +412,16 @@ def run_ours(args):
         prefill_breakdown = None
         if args.kernel_table:
             prefill_breakdown = kernel_breakdown((lambda: pg.replay()) if pg is not None else (lambda: model.prefill(ids)))
-        prefill = {"model": f"llama3-8b shape, {layers_n} layers, random init, tp{world}", "batch": 1, "seq_len": m,
-                   "ms": round(ms_prefill, 3), "tokens_per_s": round(m / (ms_prefill * 1e-3), 1),
+        prefill = {"model": f"{args.prefill_model} shape, {pcfg.layers} layers, random init, tp{world}", "batch": p_batch,
+                   "seq_len": p_seq, "ms": round(ms_prefill, 3),
+                   "tokens_per_s": round(p_batch * p_seq / (ms_prefill * 1e-3), 1),
                    "launch": "eager" if pg is None else "one CUDA graph"}
         if prefill_breakdown is not None:
             prefill["kernel_breakdown"] = prefill_breakdown
         if pg is not None:
             pg.reset()
         del model
-        if args.compare and world == 1:
+        if args.compare and world == 1 and args.prefill_model == "llama3_8b" and p_batch == 1 and p_seq == m:
             # the same stack with this project's dense-NVFP4 path and with plain bf16 linears
             for mode in ("NVFP4", "BF16"):
                 torch.cuda.empty_cache()
@@ -696,6 +701,10 @@ def main():
     ap.add_argument("--ref-tokens", type=int, default=128)
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--prefill-steps", type=int, default=3, help="0 skips the whole-model prefill measurement")
+    ap.add_argument("--prefill-model", default="llama3_8b", choices=["llama3_8b", "qwen25_7b", "mixtral_8x7b"],
+                    help="architecture of the whole-model prefill measurement (random weights)")
+    ap.add_argument("--prefill-batch", type=int, default=1)
+    ap.add_argument("--prefill-seq", type=int, default=0, help="sequence length of the prefill (0 = --tokens)")
     ap.add_argument("--compare", action="store_true", help="also time the prefill with dense NVFP4 and bf16 linears (1 GPU)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph replay")
     ap.add_argument("--shape-sweep", action="store_true",

@@ -42,10 +42,17 @@ class DecoderConfig:
     rope_theta: float = 5e5
     eps: float = 1e-6
     qkv_bias: bool = False
+    experts: int = 0  # > 0: sparse mixture-of-experts FFN (Mixtral): `experts` FFNs, `top_k` per token
+    top_k: int = 2
 
     @staticmethod
     def llama3_8b(**kw):
         return DecoderConfig(**kw)
+
+    @staticmethod
+    def mixtral_8x7b(**kw):
+        return DecoderConfig(hidden=4096, layers=32, heads=32, kv_heads=8, head_dim=128, ffn=14336, vocab=32000,
+                             rope_theta=1e6, eps=1e-5, experts=8, top_k=2, **kw)
 
     @staticmethod
     def qwen25_7b(**kw):
@@ -100,14 +107,37 @@ class SharqDecoderLayer(torch.nn.Module):
         self.qkv = _local_column(torch.cat((wq[qb:qe], wk[kb:ke], wv[kb:ke])), torch.cat((wq, wk, wv)), bias)
         wo = rnd(h, cfg.heads * d)
         self.o_proj = RowParallelSharqLinear(wo)
-        wg, wu = rnd(cfg.ffn, h), rnd(cfg.ffn, h)
         fb, fe = shard_bounds(cfg.ffn, world, rank, 128)
-        self.gate_up = _local_column(torch.cat((wg[fb:fe], wu[fb:fe])), torch.cat((wg, wu)), None)
-        wd = rnd(h, cfg.ffn)
-        self.down = RowParallelSharqLinear(wd)
-        if keep_reference:
-            self.ref = dict(qkv=torch.cat((wq, wk, wv)), qkv_bias=bias, o=wo, gate=wg, up=wu, down=wd)
-        del wq, wk, wv, wo, wg, wu, wd
+        if cfg.experts > 0:
+            # Mixtral FFN (model/qMixtralLayer.py:166-234): a bf16 router and `experts` SwiGLU FFNs;
+            # w1 | w3 share one prepared activation (here one merged GEMM), w2 takes the
+            # SwiGLU-fused prepare.  Tensor parallelism shards every expert's FFN width; the
+            # partial outputs of all experts are summed over ranks once per layer.
+            if mode != "SHARQ":
+                raise ValueError("the mixture-of-experts layer has no NVFP4 / BF16 comparison mode")
+            self.router = rnd(cfg.experts, h)
+            self.experts = []
+            ref_experts = []
+            for _ in range(cfg.experts):
+                wg, wu, wd = rnd(cfg.ffn, h), rnd(cfg.ffn, h), rnd(h, cfg.ffn)
+                gate_up = _local_column(torch.cat((wg[fb:fe], wu[fb:fe])), torch.cat((wg, wu)), None)
+                down = _local_column(wd[:, fb:fe].contiguous(), wd, None)
+                self.experts.append((gate_up, down))
+                if keep_reference:
+                    ref_experts.append((wg, wu, wd))
+                del wg, wu, wd
+            self.gate_up = self.down = None
+            if keep_reference:
+                self.ref = dict(qkv=torch.cat((wq, wk, wv)), qkv_bias=bias, o=wo, experts=ref_experts)
+            del wq, wk, wv, wo
+        else:
+            wg, wu = rnd(cfg.ffn, h), rnd(cfg.ffn, h)
+            self.gate_up = _local_column(torch.cat((wg[fb:fe], wu[fb:fe])), torch.cat((wg, wu)), None)
+            wd = rnd(h, cfg.ffn)
+            self.down = RowParallelSharqLinear(wd)
+            if keep_reference:
+                self.ref = dict(qkv=torch.cat((wq, wk, wv)), qkv_bias=bias, o=wo, gate=wg, up=wu, down=wd)
+            del wq, wk, wv, wo, wg, wu, wd
         if mode == "NVFP4":
             # dense NVFP4 baseline: unfused RMSNorm, dense activation quantisation, dense GEMM
             from .qlinear import QLinearLayer
@@ -157,6 +187,12 @@ class SharqDecoderLayer(torch.nn.Module):
         attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
         attn2 = attn.transpose(1, 2).reshape(b * s, self.local_heads * cfg.head_dim)
         o = self.o_proj(attn2)
+        if cfg.experts > 0:
+            x2 = x2 + o
+            d = self._moe(_rmsnorm(x2, self.post_norm, cfg.eps))
+            if return_delta:
+                return x2.view(b, s, h), d.view(b, s, h)
+            return (x2 + d).view(b, s, h)
         if self.fused_glue:
             prep, x2 = self.gate_up.prepare_input_add_rmsnorm(x2, o, self.post_norm, cfg.eps)
         else:
@@ -171,6 +207,42 @@ class SharqDecoderLayer(torch.nn.Module):
         if return_delta:
             return x2.view(b, s, h), d.view(b, s, h)
         return (x2 + d).view(b, s, h)
+
+    @torch.no_grad()
+    def _moe(self, hn: torch.Tensor) -> torch.Tensor:
+        """Sparse mixture of experts on the normalised hidden state [M, h] (routing as in
+        model/qMixtralLayer.py:205-234): softmax over the router logits in float, top-k,
+        renormalised weights in bf16; every expert runs on the tokens routed to it."""
+        from . import tp
+
+        cfg = self.cfg
+        m, h = hn.shape
+        routing, selected = _route(hn, self.router, cfg.top_k)
+        buf = tp.sum_buffer(None, hn.device, m * h * 2) if self.world > 1 else None
+        if buf is not None:
+            slot, out = buf.take(m, h)
+            out.zero_()
+        else:
+            out = torch.zeros((m, h), dtype=torch.bfloat16, device=hn.device)
+        mask = F.one_hot(selected, num_classes=cfg.experts).permute(2, 1, 0)
+        for e, (gate_up, down) in enumerate(self.experts):
+            idx, top_x = torch.where(mask[e])
+            if top_x.numel() == 0:
+                continue
+            cur = hn[top_x].contiguous()
+            gu = gate_up.apply_prepared(gate_up.prepare_input(cur))
+            if self.fused_glue:
+                y = down.apply_prepared(down.prepare_input_swiglu(gu))
+            else:
+                f = gu.shape[1] // 2
+                y = down.apply_prepared(down.prepare_input((F.silu(gu[:, :f]) * gu[:, f:]).contiguous()))
+            out.index_add_(0, top_x, y * routing[top_x, idx, None])
+        if self.world > 1:
+            if buf is not None:
+                buf.sum_(slot, m * h * 2)
+            else:
+                tp.all_reduce_sum_(out)
+        return out
 
     @torch.no_grad()
     def _forward_nvfp4(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
@@ -204,12 +276,36 @@ class SharqDecoderLayer(torch.nn.Module):
         attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
         x2 = x2 + F.linear(attn.transpose(1, 2).reshape(b * s, nq), r["o"])
         y = norm(x2, self.post_norm)
+        if cfg.experts > 0:
+            routing, selected = _route(y, self.router, cfg.top_k)
+            out = torch.zeros_like(y)
+            mask = F.one_hot(selected, num_classes=cfg.experts).permute(2, 1, 0)
+            for e, (wg, wu, wd) in enumerate(r["experts"]):
+                idx, top_x = torch.where(mask[e])
+                if top_x.numel():
+                    cur = y[top_x]
+                    out.index_add_(0, top_x, F.linear(F.silu(F.linear(cur, wg)) * F.linear(cur, wu), wd)
+                                   * routing[top_x, idx, None])
+            return (x2 + out).view(b, s, h)
         if glue:
             hmid = _swiglu(F.linear(y, r["gate_up"]), True)
         else:
             hmid = F.silu(F.linear(y, r["gate"])) * F.linear(y, r["up"])
         x2 = x2 + F.linear(hmid, r["down"])
         return x2.view(b, s, h)
+
+
+def _rmsnorm(t: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    tf = t.float()
+    return (tf * torch.rsqrt(tf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(torch.bfloat16)
+
+
+def _route(hn: torch.Tensor, router: torch.Tensor, top_k: int):
+    """(weights [M, top_k] bf16, expert ids [M, top_k])."""
+    weights = F.softmax(F.linear(hn, router), dim=1, dtype=torch.float)
+    weights, selected = torch.topk(weights, top_k, dim=-1)
+    weights = weights / weights.sum(dim=-1, keepdim=True)
+    return weights.to(hn.dtype), selected
 
 
 def _split_heads(qkv: torch.Tensor, b: int, s: int, heads: int, kv_heads: int, d: int, cos: torch.Tensor,
