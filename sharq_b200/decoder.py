@@ -51,13 +51,13 @@ class DecoderConfig:
 
     @staticmethod
     def mixtral_8x7b(**kw):
-        return DecoderConfig(hidden=4096, layers=32, heads=32, kv_heads=8, head_dim=128, ffn=14336, vocab=32000,
-                             rope_theta=1e6, eps=1e-5, experts=8, top_k=2, **kw)
+        return DecoderConfig(**{**dict(hidden=4096, layers=32, heads=32, kv_heads=8, head_dim=128, ffn=14336, vocab=32000,
+                                       rope_theta=1e6, eps=1e-5, experts=8, top_k=2), **kw})
 
     @staticmethod
     def qwen25_7b(**kw):
-        return DecoderConfig(hidden=3584, layers=28, heads=28, kv_heads=4, head_dim=128, ffn=18944, vocab=152064,
-                             rope_theta=1e6, qkv_bias=True, **kw)
+        return DecoderConfig(**{**dict(hidden=3584, layers=28, heads=28, kv_heads=4, head_dim=128, ffn=18944, vocab=152064,
+                                       rope_theta=1e6, qkv_bias=True), **kw})
 
 
 def rope_tables(seq: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
