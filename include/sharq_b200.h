@@ -105,6 +105,11 @@ int sharq_scaled_sparse_residual_quantize_x(const void *x_bf16, int m, int n, in
  * equal sharq_scaled_sparse_residual_quantize_x(H). */
 int sharq_rope_inplace(void *x_bf16, int rows, int row_stride, int seq_len, int heads, int head_dim,
                        const void *cos_bf16, const void *sin_bf16, void *stream);
+/* sharq_scatter_add_scaled: out[rows[i], :] += y[i, :] * w[i] in bf16 with the roundings of
+ * `final.index_add_(0, rows, y * w[:, None])` (the expert loop of model/qMixtralLayer.py:228-231);
+ * out [*, width] and y [n_rows, width] contiguous bf16, rows int64 and pairwise distinct, w bf16. */
+int sharq_scatter_add_scaled(void *out_bf16, const void *y_bf16, const int64_t *rows, const void *w_bf16, int n_rows,
+                             int width, void *stream);
 int sharq_swiglu(const void *gate_up_bf16, int rows, int ffn, void *h_bf16, void *stream);
 int sharq_swiglu_sparse_residual_quantize_x(const void *gate_up_bf16, int m, int n, int k, void *h_bf16,
                                             void *workspace, size_t workspace_bytes, void *a_comp, void *e,

@@ -158,6 +158,33 @@ __global__ void __launch_bounds__(256) swiglu_absmax_kernel(const __nv_bfloat16 
   }
 }
 
+// Expert output back into the token-major buffer of a mixture-of-experts layer:
+// out[rows[i], :] = bf16(out[rows[i], :] + bf16(y[i, :] * w[i])), rounded like the ATen
+// `index_add_(0, rows, y * w[:, None])`.  A token reaches an expert at most once, so the rows of
+// one call are distinct and no atomics are needed.
+__global__ void __launch_bounds__(256) scatter_add_scaled_kernel(__nv_bfloat16 *__restrict__ out,
+                                                                 const __nv_bfloat16 *__restrict__ y,
+                                                                 const long long *__restrict__ rows,
+                                                                 const __nv_bfloat16 *__restrict__ w, long long n_rows,
+                                                                 int width) {
+  const int vecs = width >> 3;
+  for (long long r = blockIdx.x; r < n_rows; r += gridDim.x) {
+    const float wr = __bfloat162float(w[r]);
+    const uint4 *src = reinterpret_cast<const uint4 *>(y + r * (long long)width);
+    uint4 *dst = reinterpret_cast<uint4 *>(out + rows[r] * (long long)width);
+    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+      const uint4 a4 = __ldg(src + v);
+      const uint4 o4 = dst[v];
+      const uint32_t a[4] = {a4.x, a4.y, a4.z, a4.w}, o[4] = {o4.x, o4.y, o4.z, o4.w};
+      uint32_t res[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        res[j] = pack2(lo_f(o[j]) + round_bf16(__fmul_rn(lo_f(a[j]), wr)), hi_f(o[j]) + round_bf16(__fmul_rn(hi_f(a[j]), wr)));
+      dst[v] = make_uint4(res[0], res[1], res[2], res[3]);
+    }
+  }
+}
+
 int sm_count() {
   static int sms[64] = {};
   int dev = 0;
@@ -182,6 +209,17 @@ cudaError_t run_rope_inplace(void *x, long long rows, long long row_stride, int 
   rope_kernel<<<grid_for(items), 256, 0, stream>>>(static_cast<__nv_bfloat16 *>(x), rows, row_stride, seq_len, heads,
                                                    head_dim, static_cast<const __nv_bfloat16 *>(cos_t),
                                                    static_cast<const __nv_bfloat16 *>(sin_t));
+  return cudaGetLastError();
+}
+
+cudaError_t run_scatter_add_scaled(void *out, const void *y, const long long *rows, const void *w, long long n_rows,
+                                   int width, cudaStream_t stream) {
+  long long ctas = (long long)sm_count() * 8;
+  if (ctas > n_rows) ctas = n_rows;
+  if (ctas < 1) return cudaSuccess;
+  scatter_add_scaled_kernel<<<(unsigned)ctas, 256, 0, stream>>>(static_cast<__nv_bfloat16 *>(out),
+                                                                static_cast<const __nv_bfloat16 *>(y), rows,
+                                                                static_cast<const __nv_bfloat16 *>(w), n_rows, width);
   return cudaGetLastError();
 }
 

@@ -14,4 +14,8 @@ cudaError_t run_rope_inplace(void *x, long long rows, long long row_stride, int 
 cudaError_t run_swiglu_absmax(const void *gate_up, long long rows, int ffn, long long row_stride, void *h,
                               unsigned int *amax_bits, cudaStream_t stream);
 
+// out[rows[i], :] += y[i, :] * w[i] in bf16 (distinct rows; width a multiple of 8).
+cudaError_t run_scatter_add_scaled(void *out, const void *y, const long long *rows, const void *w, long long n_rows,
+                                   int width, cudaStream_t stream);
+
 }  // namespace sharq

@@ -236,7 +236,12 @@ class SharqDecoderLayer(torch.nn.Module):
             else:
                 f = gu.shape[1] // 2
                 y = down.apply_prepared(down.prepare_input((F.silu(gu[:, :f]) * gu[:, f:]).contiguous()))
-            out.index_add_(0, top_x, y * routing[top_x, idx, None])
+            if self.fused_glue:
+                from . import ops
+
+                ops.scatter_add_scaled_(out, y, top_x.contiguous(), routing[top_x, idx].contiguous())
+            else:
+                out.index_add_(0, top_x, y * routing[top_x, idx, None])
         if self.world > 1:
             if buf is not None:
                 buf.sum_(slot, m * h * 2)

@@ -235,6 +235,24 @@ def rope_inplace_(qkv: torch.Tensor, heads: int, head_dim: int, cos: torch.Tenso
     return qkv
 
 
+def scatter_add_scaled_(out: torch.Tensor, y: torch.Tensor, rows: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """out[rows[i]] += y[i] * w[i] (bf16, rows int64 and distinct): `out.index_add_(0, rows, y * w[:, None])`
+    of the mixture-of-experts loop in one pass."""
+    _check(out.is_cuda and out.dtype == torch.bfloat16 and out.dim() == 2 and out.is_contiguous(),
+           "out must be a contiguous CUDA bfloat16 matrix")
+    _check(y.is_cuda and y.dtype == torch.bfloat16 and y.dim() == 2 and y.is_contiguous() and y.shape[1] == out.shape[1],
+           "y must be a contiguous CUDA bfloat16 matrix as wide as out")
+    _check(rows.is_cuda and rows.dtype == torch.int64 and rows.is_contiguous() and rows.numel() == y.shape[0],
+           "rows must be a contiguous CUDA int64 vector with one entry per row of y")
+    _check(w.is_cuda and w.dtype == torch.bfloat16 and w.is_contiguous() and w.numel() == y.shape[0],
+           "w must be a contiguous CUDA bfloat16 vector with one entry per row of y")
+    _check(out.shape[1] % 8 == 0, "width must be a multiple of 8")
+    with _on_device(out.device):
+        _lib.check(_lib.lib().sharq_scatter_add_scaled(_ptr(out), _ptr(y), _ptr(rows), _ptr(w), int(y.shape[0]),
+                                                       int(out.shape[1]), _stream(out.device)))
+    return out
+
+
 def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     """silu(gate) * up of a contiguous bf16 [M, 2F] activation (gate columns first) -> bf16 [M, F]."""
     _check(gate_up.is_cuda and gate_up.dtype == torch.bfloat16 and gate_up.dim() == 2 and gate_up.is_contiguous(),

@@ -90,3 +90,16 @@ def test_add_rmsnorm_prepare_equals_two_step(m, k):
     assert torch.equal(got[6], total)
     for name, a, b in zip(("a_comp", "e", "sfa", "q_res", "sf_res", "scale"), got[:6], want):
         assert torch.equal(a.reshape(-1), b.reshape(-1)), name
+
+
+def test_scatter_add_scaled_equals_aten():
+    from sharq_b200 import ops
+
+    g = torch.Generator().manual_seed(4)
+    out0 = torch.randn(1000, 512, generator=g).to(torch.bfloat16).cuda()
+    rows = torch.randperm(1000, generator=g)[:300].cuda()
+    y = torch.randn(300, 512, generator=g).to(torch.bfloat16).cuda()
+    w = torch.rand(300, generator=g).to(torch.bfloat16).cuda()
+    want = out0.clone().index_add_(0, rows, y * w[:, None])
+    got = ops.scatter_add_scaled_(out0.clone(), y, rows, w)
+    assert torch.equal(got, want)
