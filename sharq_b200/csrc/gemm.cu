@@ -18,8 +18,11 @@
 //              (tcgen05.cp), then issues 2 sparse (K=128) and 4 dense (K=64) MMAs per stage
 //              into the same accumulator; tcgen05.commit releases the stage.
 //   warps 2-9  epilogue: pull the whole accumulator into registers with tcgen05.ld, hand the
-//              tensor memory back to the MMA warp at once, then alpha/beta/bias, bf16 and the
+//              tensor memory back to the MMA warp at once, then alpha/beta/bias, bf16 (packed
+//              conversions), a transpose through a small shared-memory tile and coalesced
 //              global stores overlap the next tile's MMAs.
+// Small M with caller scratch: K is split over the SMs, units add fp32 partial sums into the
+// scratch and splitk_finalize_kernel applies the epilogue.
 // CTA-pair mode (cta_group::2, cluster of 2): the pair computes a 256 x 256 tile; CTA r owns
 // rows [128r,128r+128) (its A operands, scales, metadata, accumulator) and loads weight rows
 // [128r,128r+128) of the tile; the tensor cores of both SMs read both halves.  Every CTA
