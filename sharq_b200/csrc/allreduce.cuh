@@ -8,7 +8,7 @@ namespace sharq {
 
 constexpr int kAllReduceMaxRanks = 16;
 constexpr int kAllReduceMaxCtas = 256;
-constexpr int kAllReduceDefaultCtas = 96;
+constexpr int kAllReduceDefaultCtas = 64;
 
 // bytes of flag words every rank must provide (zero-initialised once) next to its buffer
 size_t allreduce_flag_bytes();
