@@ -214,6 +214,12 @@ const char *sharq_noalloc_last_error(void);
 int sharq_allreduce_bf16_multimem(void *multicast_data, void *const *rank_flag_ptrs, int rank, int world,
                                   size_t n_bytes, int max_ctas, int *error_flag, void *stream);
 size_t sharq_allreduce_flag_bytes(void);
+/* The same sum with plain peer loads and stores instead of the multicast object, for
+ * world <= 4 (it moves fewer bytes per link than the in-switch form at world == 2):
+ * rank_data_ptrs[p] = rank p's copy of the buffer as mapped in this process.  Rank r sums
+ * slice r of all copies in rank order (fp32) and writes the bf16 result into every copy. */
+int sharq_allreduce_bf16_peer(void *const *rank_data_ptrs, void *const *rank_flag_ptrs, int rank, int world,
+                              size_t n_bytes, int max_ctas, int *error_flag, void *stream);
 
 /* Test/tuning hook: force the GEMM kernel variant (0 = automatic; 128 or 256 = single-CTA kernel
  * with that tile width; 512 = CTA-pair kernel, 256 x 256 tile per pair).  Process-wide. */

@@ -51,6 +51,7 @@ SIGNATURES = {
     "sharq_set_gemm_tile_n": (c_int, [c_int]),
     "sharq_allreduce_bf16_multimem": (c_int, [_P, POINTER(c_void_p), c_int, c_int, c_size_t, c_int, _P, _P]),
     "sharq_allreduce_flag_bytes": (c_size_t, []),
+    "sharq_allreduce_bf16_peer": (c_int, [POINTER(c_void_p), POINTER(c_void_p), c_int, c_int, c_size_t, c_int, _P, _P]),
     "sharq_fused_rmsnorm_sparse_residual_quantize_x_noalloc": (
         c_int, [_P, _P, c_float, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P]),
     "sharq_noalloc_max_rows": (c_int, []),

@@ -17,6 +17,8 @@
 // memory, so a captured launch can be replayed.  Every spin is bounded: when the limit
 // passes the kernel records an error code and goes on (the result is then wrong, and the
 // host sees the code), it never hangs.
+#include <cuda_bf16.h>
+
 #include <cstdint>
 
 #include "allreduce.cuh"
@@ -30,6 +32,7 @@ constexpr int kUnroll = 4;
 constexpr long long kSpinLimitCycles = 4000000000LL;  // about two seconds
 
 struct AllReduceParams {
+  uint8_t *data[kAllReduceMaxRanks];      // peer-copy variant: rank p's buffer as mapped here
   uint8_t *mc;                            // multicast address of the data
   uint32_t *flags[kAllReduceMaxRanks];    // flags[p]: rank p's flag words as mapped here
   int rank, world;
@@ -80,6 +83,71 @@ __device__ __forceinline__ void cross_rank_barrier(const AllReduceParams &p, uin
   __syncthreads();
 }
 
+__device__ __forceinline__ uint4 ld_sys_16(const uint8_t *addr) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(addr)
+               : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void st_sys_16(uint8_t *addr, const uint4 &v) {
+  asm volatile("st.relaxed.sys.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+__device__ __forceinline__ void add_bf16x2(float (&acc)[8], const uint4 &v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    acc[2 * i] += __uint_as_float(w[i] << 16);
+    acc[2 * i + 1] += __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+
+// The same all-reduce with plain peer loads and stores instead of the switch's multicast
+// object: rank r sums slice r of every rank's copy in rank order (fp32) and writes the bf16
+// result into every copy.  With two ranks this moves fewer bytes per link than the in-switch
+// form (a multicast store also loops back to its sender); it is used for world == 2.
+__global__ void __launch_bounds__(kThreads) allreduce_peer_kernel(const AllReduceParams p) {
+  uint32_t *my_epoch = p.flags[p.rank] + (size_t)kAllReduceMaxCtas * kAllReduceMaxRanks + blockIdx.x;
+  const uint32_t epoch = *my_epoch;
+  cross_rank_barrier(p, epoch + 1, 0x200 + 1);
+  const size_t base = (size_t)p.rank * p.slice_bytes;
+  const size_t stride = (size_t)gridDim.x * kThreads * 16;
+  for (size_t off = ((size_t)blockIdx.x * kThreads + threadIdx.x) * 16; off < p.slice_bytes; off += kUnroll * stride) {
+    uint4 v[kUnroll][kAllReducePeerMaxRanks];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+      if (off + u * stride < p.slice_bytes)
+#pragma unroll
+        for (int r = 0; r < kAllReducePeerMaxRanks; ++r)
+          if (r < p.world) v[u][r] = ld_sys_16(p.data[r] + base + off + u * stride);
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if (off + u * stride < p.slice_bytes) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < kAllReducePeerMaxRanks; ++r)
+          if (r < p.world) add_bf16x2(acc, v[u][r]);
+        uint4 out;
+        uint32_t *o = reinterpret_cast<uint32_t *>(&out);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          __nv_bfloat162 pair = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+          o[i] = *reinterpret_cast<uint32_t *>(&pair);
+        }
+#pragma unroll
+        for (int r = 0; r < kAllReducePeerMaxRanks; ++r)
+          if (r < p.world) st_sys_16(p.data[r] + base + off + u * stride, out);
+      }
+    }
+  }
+  cross_rank_barrier(p, epoch + 2, 0x200 + 2);
+  if (threadIdx.x == 0) *my_epoch = epoch + 2;
+}
+
 __global__ void __launch_bounds__(kThreads) allreduce_multimem_kernel(const AllReduceParams p) {
   // barriers this CTA index has been through so far (same on every rank)
   uint32_t *my_epoch = p.flags[p.rank] + (size_t)kAllReduceMaxCtas * kAllReduceMaxRanks + blockIdx.x;
@@ -106,9 +174,13 @@ size_t allreduce_flag_bytes() {
   return ((size_t)kAllReduceMaxCtas * kAllReduceMaxRanks + kAllReduceMaxCtas) * sizeof(uint32_t);
 }
 
-cudaError_t run_allreduce_multimem(void *multicast_data, void *const *rank_flag_ptrs, int rank, int world, size_t bytes,
-                                   int max_ctas, int *error_flag, cudaStream_t stream) {
+cudaError_t run_allreduce(void *multicast_data, void *const *rank_data_ptrs, void *const *rank_flag_ptrs, int rank,
+                          int world, size_t bytes, int max_ctas, int *error_flag, cudaStream_t stream) {
   AllReduceParams p{};
+  const bool peer = multicast_data == nullptr;
+  if (peer && (rank_data_ptrs == nullptr || world > kAllReducePeerMaxRanks)) return cudaErrorInvalidValue;
+  if (peer)
+    for (int i = 0; i < world; ++i) p.data[i] = static_cast<uint8_t *>(rank_data_ptrs[i]);
   p.mc = static_cast<uint8_t *>(multicast_data);
   for (int i = 0; i < world; ++i) p.flags[i] = static_cast<uint32_t *>(rank_flag_ptrs[i]);
   p.rank = rank;
@@ -126,7 +198,10 @@ cudaError_t run_allreduce_multimem(void *multicast_data, void *const *rank_flag_
   if (max_ctas <= 0 || max_ctas > kAllReduceMaxCtas) max_ctas = kAllReduceDefaultCtas;
   if (ctas > (size_t)max_ctas) ctas = max_ctas;
   if (ctas < 1) ctas = 1;
-  allreduce_multimem_kernel<<<(unsigned)ctas, kThreads, 0, stream>>>(p);
+  if (peer)
+    allreduce_peer_kernel<<<(unsigned)ctas, kThreads, 0, stream>>>(p);
+  else
+    allreduce_multimem_kernel<<<(unsigned)ctas, kThreads, 0, stream>>>(p);
   return cudaGetLastError();
 }
 

@@ -226,9 +226,26 @@ int sharq_allreduce_bf16_multimem(void *multicast_data, void *const *rank_flag_p
   SHARQ_REQUIRE(n_bytes > 0 && n_bytes % ((size_t)16 * world) == 0, "n_bytes must be a positive multiple of 16 * world");
   SHARQ_REQUIRE((reinterpret_cast<uintptr_t>(multicast_data) & 15) == 0, "multicast_data must be 16-byte aligned");
   for (int i = 0; i < world; ++i) SHARQ_REQUIRE(rank_flag_ptrs[i] != nullptr, "rank_flag_ptrs[%d] is NULL", i);
-  return check_cuda(sharq::run_allreduce_multimem(multicast_data, rank_flag_ptrs, rank, world, n_bytes, max_ctas,
-                                                  error_flag, as_stream(stream)),
+  return check_cuda(sharq::run_allreduce(multicast_data, nullptr, rank_flag_ptrs, rank, world, n_bytes, max_ctas, error_flag,
+                                         as_stream(stream)),
                     "allreduce_multimem launch");
+}
+
+int sharq_allreduce_bf16_peer(void *const *rank_data_ptrs, void *const *rank_flag_ptrs, int rank, int world, size_t n_bytes,
+                              int max_ctas, int *error_flag, void *stream) {
+  SHARQ_REQUIRE(rank_data_ptrs && rank_flag_ptrs && error_flag, "rank_data_ptrs, rank_flag_ptrs, error_flag must be set");
+  SHARQ_REQUIRE(world >= 1 && world <= sharq::kAllReducePeerMaxRanks, "world must be in [1, %d]",
+                sharq::kAllReducePeerMaxRanks);
+  SHARQ_REQUIRE(rank >= 0 && rank < world, "rank must be in [0, world)");
+  SHARQ_REQUIRE(n_bytes > 0 && n_bytes % ((size_t)16 * world) == 0, "n_bytes must be a positive multiple of 16 * world");
+  for (int i = 0; i < world; ++i) {
+    SHARQ_REQUIRE(rank_data_ptrs[i] != nullptr && (reinterpret_cast<uintptr_t>(rank_data_ptrs[i]) & 15) == 0,
+                  "rank_data_ptrs[%d] must be a 16-byte aligned pointer", i);
+    SHARQ_REQUIRE(rank_flag_ptrs[i] != nullptr, "rank_flag_ptrs[%d] is NULL", i);
+  }
+  return check_cuda(sharq::run_allreduce(nullptr, rank_data_ptrs, rank_flag_ptrs, rank, world, n_bytes, max_ctas, error_flag,
+                                         as_stream(stream)),
+                    "allreduce_peer launch");
 }
 
 int sharq_set_gemm_tile_n(int tile_n) {

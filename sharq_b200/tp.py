@@ -94,6 +94,9 @@ class SymmetricSumBuffer:
         dist.barrier(group)
         flags_at = self.SLOTS * self.slot_bytes
         self.flag_ptrs = (ctypes.c_void_p * self.world)(*[b + flags_at for b in bases])
+        self.bases = bases
+        # two ranks: plain peer loads/stores move fewer bytes per link than the multicast object
+        self.peer_copy = self.world == 2 and os.environ.get("SHARQ_TP_ALLREDUCE", "auto").lower() != "multimem"
         self.handle = handle
         self._next = 0
 
@@ -109,6 +112,14 @@ class SymmetricSumBuffer:
         (max_ctas: 0 = the library's default grid limit)."""
         from . import _lib, ops
 
+        flag = ctypes.c_void_p(ops._error_flag(self.device).data_ptr())
+        stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        if self.peer_copy:
+            data = (ctypes.c_void_p * self.world)(*[b + slot * self.slot_bytes for b in self.bases])
+            with torch.cuda.device(self.device):
+                _lib.check(_lib.lib().sharq_allreduce_bf16_peer(data, self.flag_ptrs, self.rank, self.world, nbytes,
+                                                                 int(max_ctas), flag, stream))
+            return
         with torch.cuda.device(self.device):
             _lib.check(_lib.lib().sharq_allreduce_bf16_multimem(
                 ctypes.c_void_p(self.multicast + slot * self.slot_bytes), self.flag_ptrs, self.rank, self.world, nbytes,

@@ -19,9 +19,16 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
-    os.environ["SHARQ_TP_ALLREDUCE"] = "multimem"  # fail loudly instead of falling back
     ok = True
-    for m, n, k in ((256, 512, 1024), (2048, 4096, 4096), (300, 384, 2048)):
+    # "multimem": the in-switch kernel (fails loudly instead of falling back); "auto": with two
+    # ranks the peer-copy kernel
+    for mode, (m, n, k) in [(md, shape) for md in ("multimem", "auto")
+                            for shape in ((256, 512, 1024), (2048, 4096, 4096), (300, 384, 2048))]:
+        if os.environ.get("SHARQ_TP_ALLREDUCE") != mode:
+            torch.cuda.synchronize()
+            dist.barrier()
+            tp.release_sum_buffers()
+            os.environ["SHARQ_TP_ALLREDUCE"] = mode
         w = H.config0_w(n, k, 3).to(dev)
         lin = tp.RowParallelSharqLinear(w)
         b, e = tp.shard_bounds(k, world, rank, tp.K_ALIGN)
@@ -41,7 +48,7 @@ def main():
             tol = want.abs() * 2.0 ** -7 + 1e-30
             if not bool((err <= tol).all()):
                 ok = False
-                print(f"rank {rank}: mismatch m={m} n={n} k={k} rep={rep} max err {float(err.max())}", flush=True)
+                print(f"rank {rank}: mismatch mode={mode} m={m} n={n} k={k} rep={rep} max err {float(err.max())}", flush=True)
         # every rank must hold the same bytes
         mine = lin.apply_prepared_reduced(prep).clone()
         peers = [torch.empty_like(mine) for _ in range(world)]
