@@ -82,7 +82,7 @@ def test_prepare_debug_payload(oracle):
     assert H.raw_violation_rate(got[0].reshape(m, k // 2)) == 0.0
 
 
-@pytest.mark.parametrize("m,k", [(1, 128), (37, 256), (130, 512), (512, 4096), (64, 14336)])
+@pytest.mark.parametrize("m,k", [(1, 128), (37, 256), (130, 512), (512, 4096), (64, 14336), (3, 32768)])  # 32768: K/32 = 1024, the limit
 def test_rmsnorm_prepare_matches_oracle(oracle, m, k):
     from tests.gpu_util import Buf, call, dptr, sizes5, stream_ptr
 
