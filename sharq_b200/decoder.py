@@ -27,7 +27,7 @@ from dataclasses import dataclass
 import torch
 import torch.nn.functional as F
 
-from .tp import RowParallelSharqLinear, shard_bounds
+from .tp import RowParallelSharqLinear, head_layout, padded_size, shard_bounds
 
 
 @dataclass
@@ -76,9 +76,10 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
 
 class SharqDecoderLayer(torch.nn.Module):
     def __init__(self, cfg: DecoderConfig, gen: torch.Generator, device, world: int = 1, rank: int = 0,
-                 keep_reference: bool = False, mode: str = "SHARQ", fused_glue: bool = True):
+                 keep_reference: bool = False, mode: str = "SHARQ", fused_glue: bool = True, reduce_hook=None):
         super().__init__()
         self.fused_glue = fused_glue
+        self.reduce_hook = reduce_hook
         if mode not in ("SHARQ", "NVFP4", "BF16"):
             raise ValueError(f"unknown mode {mode}")
         if mode != "SHARQ" and world != 1:
@@ -88,26 +89,39 @@ class SharqDecoderLayer(torch.nn.Module):
         self.cfg, self.world, self.rank = cfg, world, rank
         self.ref = {} if keep_reference else None  # unquantised bf16 weights (accuracy checks, baselines)
         h, d = cfg.hidden, cfg.head_dim
-        if cfg.heads % world or cfg.kv_heads % world:
-            raise ValueError(f"{cfg.heads} query / {cfg.kv_heads} KV heads do not split over {world} ranks; pad first")
-        self.local_heads, self.local_kv = cfg.heads // world, cfg.kv_heads // world
+        # heads of this rank (query ids, -1 = zero padding head; key/value ids), see tp.head_layout
+        q_ids, kv_ids = head_layout(cfg.heads, cfg.kv_heads, world)[rank]
+        self.local_heads, self.local_kv = len(q_ids), len(kv_ids)
 
         def rnd(n, k):
             return (0.02 * torch.randn(n, k, generator=gen, device=device)).to(torch.bfloat16)
 
+        def head_rows(w, ids):
+            """Rows of the heads `ids` of a [heads * d, *] matrix (or [heads * d] vector); zeros for -1."""
+            parts = [w[i * d:(i + 1) * d] if i >= 0 else torch.zeros_like(w[:d]) for i in ids]
+            return torch.cat(parts)
+
         # every rank draws the same full weights (same generator state) and keeps its shard
         wq, wk, wv = rnd(cfg.heads * d, h), rnd(cfg.kv_heads * d, h), rnd(cfg.kv_heads * d, h)
-        qb, qe = shard_bounds(cfg.heads * d, world, rank, 128)
-        kb, ke = shard_bounds(cfg.kv_heads * d, world, rank, 128)
-        bias = None
+        bias = full_bias = None
         if cfg.qkv_bias:
-            bq, bk, bv = (0.02 * torch.randn(n, generator=gen, device=device) for n in
+            bq, bk, bv = ((0.02 * torch.randn(n, generator=gen, device=device)).to(torch.bfloat16) for n in
                           (cfg.heads * d, cfg.kv_heads * d, cfg.kv_heads * d))
-            bias = torch.cat((bq[qb:qe], bk[kb:ke], bv[kb:ke])).to(torch.bfloat16)
-        self.qkv = _local_column(torch.cat((wq[qb:qe], wk[kb:ke], wv[kb:ke])), torch.cat((wq, wk, wv)), bias)
+            bias = torch.cat((head_rows(bq, q_ids), head_rows(bk, kv_ids), head_rows(bv, kv_ids)))
+            full_bias = torch.cat((bq, bk, bv))
+        self.qkv = _local_column(torch.cat((head_rows(wq, q_ids), head_rows(wk, kv_ids), head_rows(wv, kv_ids))),
+                                 torch.cat((wq, wk, wv)), bias)
         wo = rnd(h, cfg.heads * d)
-        self.o_proj = RowParallelSharqLinear(wo)
-        fb, fe = shard_bounds(cfg.ffn, world, rank, 128)
+        wo_local = torch.cat([wo[:, i * d:(i + 1) * d] if i >= 0 else torch.zeros_like(wo[:, :d]) for i in q_ids], dim=1)
+        self.o_proj = RowParallelSharqLinear(wo, local_columns=wo_local, world_rank=(world, rank), reduce_hook=reduce_hook)
+        # the FFN width is padded with zero rows / columns to world slices that are multiples of 128
+        ffn_pad = padded_size(cfg.ffn, world, 128)
+
+        def pad_rows(w):
+            return w if ffn_pad == cfg.ffn else torch.cat((w, torch.zeros((ffn_pad - cfg.ffn, w.shape[1]), dtype=w.dtype,
+                                                                      device=w.device)))
+
+        fb, fe = shard_bounds(ffn_pad, world, rank, 128)
         if cfg.experts > 0:
             # Mixtral FFN (model/qMixtralLayer.py:166-234): a bf16 router and `experts` SwiGLU FFNs;
             # w1 | w3 share one prepared activation (here one merged GEMM), w2 takes the
@@ -120,23 +134,24 @@ class SharqDecoderLayer(torch.nn.Module):
             ref_experts = []
             for _ in range(cfg.experts):
                 wg, wu, wd = rnd(cfg.ffn, h), rnd(cfg.ffn, h), rnd(h, cfg.ffn)
-                gate_up = _local_column(torch.cat((wg[fb:fe], wu[fb:fe])), torch.cat((wg, wu)), None)
-                down = _local_column(wd[:, fb:fe].contiguous(), wd, None)
+                gate_up = _local_column(torch.cat((pad_rows(wg)[fb:fe], pad_rows(wu)[fb:fe])), torch.cat((wg, wu)), None)
+                down = _local_column(pad_rows(wd.T).T[:, fb:fe].contiguous(), wd, None)
                 self.experts.append((gate_up, down))
                 if keep_reference:
                     ref_experts.append((wg, wu, wd))
                 del wg, wu, wd
             self.gate_up = self.down = None
             if keep_reference:
-                self.ref = dict(qkv=torch.cat((wq, wk, wv)), qkv_bias=bias, o=wo, experts=ref_experts)
+                self.ref = dict(qkv=torch.cat((wq, wk, wv)), qkv_bias=full_bias, o=wo, experts=ref_experts)
             del wq, wk, wv, wo
         else:
             wg, wu = rnd(cfg.ffn, h), rnd(cfg.ffn, h)
-            self.gate_up = _local_column(torch.cat((wg[fb:fe], wu[fb:fe])), torch.cat((wg, wu)), None)
+            self.gate_up = _local_column(torch.cat((pad_rows(wg)[fb:fe], pad_rows(wu)[fb:fe])), torch.cat((wg, wu)), None)
             wd = rnd(h, cfg.ffn)
-            self.down = RowParallelSharqLinear(wd)
+            self.down = RowParallelSharqLinear(wd, local_columns=pad_rows(wd.T).T[:, fb:fe], world_rank=(world, rank),
+                                               reduce_hook=reduce_hook)
             if keep_reference:
-                self.ref = dict(qkv=torch.cat((wq, wk, wv)), qkv_bias=bias, o=wo, gate=wg, up=wu, down=wd)
+                self.ref = dict(qkv=torch.cat((wq, wk, wv)), qkv_bias=full_bias, o=wo, gate=wg, up=wu, down=wd)
             del wq, wk, wv, wo, wg, wu, wd
         if mode == "NVFP4":
             # dense NVFP4 baseline: unfused RMSNorm, dense activation quantisation, dense GEMM
@@ -218,7 +233,7 @@ class SharqDecoderLayer(torch.nn.Module):
         cfg = self.cfg
         m, h = hn.shape
         routing, selected = _route(hn, self.router, cfg.top_k)
-        buf = tp.sum_buffer(None, hn.device, m * h * 2) if self.world > 1 else None
+        buf = tp.sum_buffer(None, hn.device, m * h * 2) if self.world > 1 and self.reduce_hook is None else None
         if buf is not None:
             slot, out = buf.take(m, h)
             out.zero_()
@@ -242,7 +257,9 @@ class SharqDecoderLayer(torch.nn.Module):
                 ops.scatter_add_scaled_(out, y, top_x.contiguous(), routing[top_x, idx].contiguous())
             else:
                 out.index_add_(0, top_x, y * routing[top_x, idx, None])
-        if self.world > 1:
+        if self.reduce_hook is not None:
+            out = self.reduce_hook(out)
+        elif self.world > 1:
             if buf is not None:
                 buf.sum_(slot, m * h * 2)
             else:
@@ -354,13 +371,15 @@ class SharqDecoder(torch.nn.Module):
     """Embedding -> N decoder layers -> final norm -> (bf16) lm_head on the last token."""
 
     def __init__(self, cfg: DecoderConfig, device, world: int = 1, rank: int = 0, seed: int = 0,
-                 keep_reference: bool = False, mode: str = "SHARQ", fused_glue: bool = True):
+                 keep_reference: bool = False, mode: str = "SHARQ", fused_glue: bool = True, reduce_hook=None):
+        """reduce_hook: callable(partial) -> sum over ranks, used instead of the collectives (lets a
+        test run several ranks as threads of one process)."""
         super().__init__()
         self.cfg = cfg
         gen = torch.Generator(device=device).manual_seed(seed)
         self.embed = (0.02 * torch.randn(cfg.vocab, cfg.hidden, generator=gen, device=device)).to(torch.bfloat16)
-        self.layers = torch.nn.ModuleList([SharqDecoderLayer(cfg, gen, device, world, rank, keep_reference, mode, fused_glue)
-                                           for _ in range(cfg.layers)])
+        self.layers = torch.nn.ModuleList([SharqDecoderLayer(cfg, gen, device, world, rank, keep_reference, mode, fused_glue,
+                                                             reduce_hook) for _ in range(cfg.layers)])
         self.final_norm = (1 + 0.1 * torch.randn(cfg.hidden, generator=gen, device=device)).to(torch.bfloat16)
         self.lm_head = (0.02 * torch.randn(cfg.vocab, cfg.hidden, generator=gen, device=device)).to(torch.bfloat16)
 

@@ -56,6 +56,28 @@ def padded_size(total: int, world: int, align: int) -> int:
     return (total + unit - 1) // unit * unit
 
 
+def head_layout(heads: int, kv_heads: int, world: int):
+    """Attention heads of every rank: a list of (query head ids, key/value head ids); a query id of
+    -1 is a padding head (zero weights).  When both counts divide by `world` the heads are cut
+    contiguously.  Otherwise, if `world` is a multiple of `kv_heads`, every KV head is replicated
+    on world / kv_heads consecutive ranks and its query group is dealt to them in equal parts,
+    padded at the end (Qwen2.5-7B on 8 ranks: 28 query / 4 KV heads -> 4 + 3(+1 pad) query heads
+    on the two ranks of each KV head)."""
+    if heads % world == 0 and kv_heads % world == 0:
+        hq, hk = heads // world, kv_heads // world
+        return [(list(range(r * hq, (r + 1) * hq)), list(range(r * hk, (r + 1) * hk))) for r in range(world)]
+    if world % kv_heads or heads % kv_heads:
+        raise ValueError(f"{heads} query / {kv_heads} KV heads cannot be laid out over {world} ranks")
+    rep, group = world // kv_heads, heads // kv_heads
+    per_rank = (group + rep - 1) // rep
+    out = []
+    for r in range(world):
+        j, i = r // rep, r % rep
+        ids = [j * group + i * per_rank + t if i * per_rank + t < group else -1 for t in range(per_rank)]
+        out.append((ids, [j]))
+    return out
+
+
 def scaled_weight(weight: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """Full weight divided by its global tensor scale (bf16), and that scale."""
     scale = torch.clamp(weight.abs().max().float() / (448.0 * 6.0), min=1e-9)
@@ -212,23 +234,40 @@ class RowParallelSharqLinear(_ShardedBase):
     """Shards in_features.  forward takes this rank's [M, K/world] slice of the activation
     and returns the all-reduced [M, N] output."""
 
-    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, group=None, fused_gemm: bool = True):
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, group=None, fused_gemm: bool = True,
+                 local_columns: Optional[torch.Tensor] = None, world_rank: Optional[Tuple[int, int]] = None,
+                 reduce_hook=None):
+        """weight: the full [N, K] matrix (its absmax gives the tensor scale).  local_columns:
+        this rank's [N, K_local] part when it is not the contiguous K / world slice (padded or
+        regrouped layouts).  world_rank: (world, rank) instead of the process group's.
+        reduce_hook: callable(partial) -> sum, used instead of the collective (tests that run
+        several ranks in one process)."""
         super().__init__(group)
         from . import ops
         from .qlinear import QLinearLayer
 
+        if world_rank is not None:
+            self.world, self.rank = int(world_rank[0]), int(world_rank[1])
+        self.reduce_hook = reduce_hook
         n, k = weight.shape
-        b, e = shard_bounds(k, self.world, self.rank, K_ALIGN)
-        w_scaled, scale = scaled_weight(weight)
-        q, sfs, sfd = ops.quantize_w32_shared(w_scaled[:, b:e].contiguous())
-        self.local = QLinearLayer.from_quantized(e - b, n, q, sfs, sfd, scale, bias=None, fused_gemm=fused_gemm)
+        scale = torch.clamp(weight.abs().max().float() / (448.0 * 6.0), min=1e-9)
+        if local_columns is None:
+            b, e = shard_bounds(k, self.world, self.rank, K_ALIGN)
+            local_columns = weight[:, b:e]
+        if local_columns.shape[1] % K_ALIGN:
+            raise ValueError(f"per-rank input size {local_columns.shape[1]} is not a multiple of {K_ALIGN}")
+        q, sfs, sfd = ops.quantize_w32_shared((local_columns / scale).to(torch.bfloat16).contiguous())
+        self.local = QLinearLayer.from_quantized(int(local_columns.shape[1]), n, q, sfs, sfd, scale, bias=None,
+                                                 fused_gemm=fused_gemm)
         if bias is not None:
             self.register_buffer("bias", bias.to(q.device, torch.bfloat16))
         else:
             self.bias = None
 
     def reduce(self, y_partial: torch.Tensor) -> torch.Tensor:
-        if self.world > 1:
+        if self.reduce_hook is not None:
+            y_partial = self.reduce_hook(y_partial)
+        elif self.world > 1:
             dist.all_reduce(y_partial, op=dist.ReduceOp.SUM, group=self.group)
         if self.bias is not None:
             y_partial = y_partial + self.bias
@@ -239,7 +278,7 @@ class RowParallelSharqLinear(_ShardedBase):
         the partial sums go straight into symmetric memory and are reduced in the switch; the
         returned tensor is then a view of a shared slot (valid until SymmetricSumBuffer.SLOTS
         more row-parallel layers of the group have run)."""
-        if self.world == 1:
+        if self.world == 1 or self.reduce_hook is not None:
             return self.reduce(self.local.apply_prepared(prepared))
         m, n = int(prepared[4].shape[0]) if prepared[0] == "SHARQ" else 0, self.local.out_features
         nbytes = m * n * 2

@@ -56,3 +56,59 @@ def test_small_moe_decoder_tracks_bf16_reference():
     assert cos > 0.97, float(cos)
     plain = SharqDecoder(cfg, torch.device("cuda"), seed=5, fused_glue=False).prefill(ids)
     assert torch.equal(got, plain)  # SwiGLU fused into the w2 prepare changes no bit
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_padded_tensor_parallel_layout_matches_single_rank(world):
+    """A Qwen-like shape that does not divide (7 query heads on 1 KV head, FFN 1920): the KV
+    head is replicated, query heads are dealt with zero padding heads, the FFN is padded with
+    zero rows.  The ranks run as threads of this process on one GPU and exchange their partial
+    sums on the host (no collective, no kernel waits on another); the result must track the
+    single-rank model."""
+    import threading
+
+    from sharq_b200 import ops
+    from sharq_b200.decoder import DecoderConfig, SharqDecoder
+
+    cfg = DecoderConfig(hidden=896, layers=2, heads=7, kv_heads=1, head_dim=128, ffn=1920, vocab=1500, qkv_bias=True)
+    dev = torch.device("cuda")
+    ids = torch.randint(0, cfg.vocab, (2, 96), generator=torch.Generator().manual_seed(3)).cuda()
+    want = SharqDecoder(cfg, dev, seed=11).prefill(ids)
+
+    barrier = threading.Barrier(world)
+    parts, results, errors = [None] * world, [None] * world, []
+
+    def hook_for(rank):
+        def hook(t):
+            torch.cuda.synchronize()
+            parts[rank] = t
+            barrier.wait()
+            total = torch.stack([p.float() for p in parts]).sum(0).to(torch.bfloat16)
+            torch.cuda.synchronize()
+            barrier.wait()
+            return total
+        return hook
+
+    def run(rank):
+        try:
+            torch.cuda.set_device(0)
+            model = SharqDecoder(cfg, dev, world=world, rank=rank, seed=11, reduce_hook=hook_for(rank))
+            results[rank] = model.prefill(ids)
+            torch.cuda.synchronize()
+        except Exception as exc:  # release the others instead of leaving them at the barrier
+            errors.append(exc)
+            barrier.abort()
+
+    threads = [threading.Thread(target=run, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=300)
+    assert not errors, errors
+    ops.check_device_errors()
+    for r in range(1, world):
+        assert torch.equal(results[r], results[0])  # every rank ends with the same logits
+    got = results[0]
+    cos = torch.nn.functional.cosine_similarity(got.flatten(), want.flatten(), dim=0)
+    rel = (got - want).norm() / want.norm()
+    assert cos > 0.99 and rel < 0.15, (float(cos), float(rel))

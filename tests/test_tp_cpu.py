@@ -70,3 +70,23 @@ def test_column_then_row_parallel_all_reduce_gloo():
     assert len(out) == world
     for r in range(world):
         assert out[r] < 1e-5
+
+
+def test_head_layout_for_non_divisible_models():
+    from sharq_b200.tp import head_layout, padded_size
+
+    # Llama-3-8B on 8 ranks: contiguous
+    lay = head_layout(32, 8, 8)
+    assert lay[3] == ([12, 13, 14, 15], [3])
+    # Qwen2.5-7B on 8 ranks: 28 query / 4 KV heads -> KV heads on two ranks each, 4 + 3 (+1 pad) query heads
+    lay = head_layout(28, 4, 8)
+    assert lay[0] == ([0, 1, 2, 3], [0]) and lay[1] == ([4, 5, 6, -1], [0]) and lay[7] == ([25, 26, 27, -1], [3])
+    real = sorted(i for ids, _ in lay for i in ids if i >= 0)
+    assert real == list(range(28))  # every query head exactly once
+    for ids, kv in lay:  # a rank's query heads all belong to its KV head
+        assert all(i // 7 == kv[0] for i in ids if i >= 0)
+    assert head_layout(28, 4, 4)[2] == (list(range(14, 21)), [2])
+    assert padded_size(18944, 8, 128) == 19456 and padded_size(18944, 4, 128) == 18944
+    import pytest
+    with pytest.raises(ValueError):
+        head_layout(28, 4, 3)
