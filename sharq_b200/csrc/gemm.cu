@@ -248,6 +248,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const int unit0 = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int unit_stride = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
+  if (threadIdx.x == 32) {
+    // fetch the tensor maps while the barriers and tensor memory are being set up
+    ptx::tma_prefetch_desc(&tm_w);
+    if (DENSE) ptx::tma_prefetch_desc(&tm_a_dense);
+    if (SPARSE) ptx::tma_prefetch_desc(&tm_a_comp);
+  }
   if (threadIdx.x == 0) {
     TIMING_STAMP(0);
     for (int s = 0; s < S; ++s) {
@@ -274,9 +280,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (ptx::elect_one()) {
-      ptx::tma_prefetch_desc(&tm_w);
-      if (DENSE) ptx::tma_prefetch_desc(&tm_a_dense);
-      if (SPARSE) ptx::tma_prefetch_desc(&tm_a_comp);
       uint32_t g = 0;  // stages issued so far, across tiles
       bool ok = true;
       for (int u = unit0; u < num_units && ok; u += unit_stride) {
