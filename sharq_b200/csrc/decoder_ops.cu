@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(256) swiglu_absmax_kernel(const __nv_bfloat16 
                                                             unsigned int *__restrict__ amax_bits) {
   __shared__ float warp_max[8];
   const int vecs = ffn >> 3;
-  float mx = 0.0f;
+  __nv_bfloat162 mx2 = __floats2bfloat162_rn(0.0f, 0.0f);  // running max of |h|, two lanes
   // a CTA walks rows, its threads the 16-byte vectors of a row, two vectors in flight per thread
   for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
     const __nv_bfloat16 *grow = gate_up + row * row_stride;
@@ -135,15 +135,15 @@ __global__ void __launch_bounds__(256) swiglu_absmax_kernel(const __nv_bfloat16 
         uint32_t o[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float a = round_bf16(__fmul_rn(silu_bf16(lo_f(gw[j])), lo_f(uw[j])));
-          const float b = round_bf16(__fmul_rn(silu_bf16(hi_f(gw[j])), hi_f(uw[j])));
-          mx = fmaxf(mx, fmaxf(fabsf(a), fabsf(b)));
-          o[j] = pack2(a, b);
+          // the product of two bf16 values is exact in float; the packed conversion rounds it once
+          o[j] = pack2(__fmul_rn(silu_bf16(lo_f(gw[j])), lo_f(uw[j])), __fmul_rn(silu_bf16(hi_f(gw[j])), hi_f(uw[j])));
+          mx2 = __hmax2(mx2, __habs2(*reinterpret_cast<__nv_bfloat162 *>(&o[j])));
         }
         *reinterpret_cast<uint4 *>(hrow + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
       }
     }
   }
+  float mx = fmaxf(__bfloat162float(mx2.x), __bfloat162float(mx2.y));
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
