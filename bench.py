@@ -452,7 +452,9 @@ def run_ours(args):
         "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": h2d_bytes,
                 "d2h_bytes_per_step": d2h_bytes, "ms_per_step": round(ms_e2e, 4),
                 "pipeline": "copies on a second stream, double-buffered: H2D of step i+1 and D2H of step i overlap kernels"},
-        "gpu_launches": args.steps * layers_n * 12,
+        # per layer: 4 linears x (statistics, prepare, GEMM) kernels, plus this project's all-reduce
+        # kernel after the two row-parallel linears when the work is sharded
+        "gpu_launches": args.steps * layers_n * (12 + (2 if world > 1 else 0)),
         "clocks": clocks,
     }
     if breakdown is not None:
