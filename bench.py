@@ -611,8 +611,11 @@ def run_shape_sweep(args):
                                                                                  wq[i][1], wq[i][2], alpha)), copies)
                 wd = [(qw_d.clone(), sfw_d.clone()) for _ in range(copies)]
                 t_dg = timed_rotating(lambda i: (lambda: ops.matmul(qx, wd[i][0], sfx, wd[i][1], alpha)), copies)
+                # the whole linear as the vLLM plugin runs it in a decode step (scaled prepare + GEMM)
+                t_lin = timed_rotating(lambda i: (lambda: ops.sharq_linear_forward(x, wq[i][0], wq[i][1], wq[i][2], 1.0)), copies)
                 del wq, wd
             else:
+                t_lin = None
                 t_gemm = timed(lambda: ops.sharq_linear_gemm(a_comp, e, sfa, q_res, sf_res, qw, sfs, sfd, alpha), iters)
                 t_dg = timed(lambda: ops.matmul(qx, qw_d, sfx, sfw_d, alpha), iters)
             ops.check_device_errors()
@@ -629,6 +632,7 @@ def run_shape_sweep(args):
                 "nvfp4_quant_us": round(t_dq, 1), "nvfp4_gemm_us": round(t_dg, 1),
                 "nvfp4_gemm_tflops": round(flops / (t_dg * 1e-6) / 1e12, 1),
                 "sharq_linear_us": round(t_prep + t_gemm, 1), "nvfp4_linear_us": round(t_dq + t_dg, 1),
+                "sharq_linear_graph_us": None if t_lin is None else round(t_lin, 1),
             })
             del x, xs, prep, a_comp, e, sfa, q_res, sf_res, qx, sfx
         del qw, sfs, sfd, qw_d, sfw_d

@@ -350,6 +350,7 @@ struct PrepareParams {
 };
 
 constexpr int kPrepareCtasPerSm = 3;
+constexpr size_t kInlineAbsmaxElements = 256 * 1024;  // up to 512 KB of input is scanned by every CTA
 
 __device__ __forceinline__ void zero_range(uint8_t *base, size_t begin, size_t end, int worker, int workers) {
   if (base == nullptr || begin >= end) return;
@@ -394,7 +395,33 @@ __global__ void __launch_bounds__(kPrepareThreads, kPrepareCtasPerSm) prepare_ke
 
   float scale = 1.0f, recip = 1.0f;
   if (kMode != 0) {
-    const float amax = __uint_as_float(*p.amax_bits);
+    float amax;
+    if (kMode == 2 && p.amax_bits == nullptr) {
+      // Small input (a decode step): every CTA finds max|x| of the whole tensor itself, which
+      // replaces the memset and the statistics launch; the tensor is read from L2.
+      __shared__ float cta_max[kWarpsPerCta];
+      const uint4 *all = reinterpret_cast<const uint4 *>(p.x);
+      const size_t n16 = (size_t)m * k / 8;
+      __nv_bfloat162 m2 = __floats2bfloat162_rn(0.0f, 0.0f);
+      for (size_t i = threadIdx.x; i < n16; i += blockDim.x) {
+        const uint4 v = __ldg(all + i);
+        m2 = __hmax2(m2, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&v.x)));
+        m2 = __hmax2(m2, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&v.y)));
+        m2 = __hmax2(m2, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&v.z)));
+        m2 = __hmax2(m2, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&v.w)));
+      }
+      float mx = fmaxf(__bfloat162float(m2.x), __bfloat162float(m2.y));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      if ((threadIdx.x & 31) == 0) cta_max[threadIdx.x >> 5] = mx;
+      __syncthreads();
+      mx = cta_max[0];
+#pragma unroll
+      for (int w = 1; w < kWarpsPerCta; ++w) mx = fmaxf(mx, cta_max[w]);
+      amax = mx;
+    } else {
+      amax = __uint_as_float(*p.amax_bits);
+    }
     // ATen divides a CUDA tensor by a host scalar by multiplying with the float
     // reciprocal; clamp(min=1e-9) follows (kernels/src/bindings.cpp:337 of the reference).
     scale = fmaxf(__fmul_rn(amax, 1.0f / 2688.0f), 1.0e-9f);
@@ -579,9 +606,13 @@ cudaError_t run_scaled_prepare(const void *x, const void *gamma, float eps, int 
                                     : reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + 256);
   cudaError_t err = cudaSuccess;
   const bool rms = gamma != nullptr;
+  // a small non-RMSNorm input (a decode step): the prepare kernel finds max|x| itself
+  const bool inline_absmax = !rms && !absmax_ready && (size_t)m * k <= kInlineAbsmaxElements;
   if (absmax_ready) {
     // the producer of x already left max|x| in the workspace: no statistics pass
     if (rms) return cudaErrorInvalidValue;
+  } else if (inline_absmax) {
+    amax_bits = nullptr;
   } else if ((err = cudaMemsetAsync(amax_bits, 0, sizeof(unsigned int), stream)) != cudaSuccess) {
     return err;
   } else if (rms) {
