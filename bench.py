@@ -239,6 +239,27 @@ def run_ours(args):
         step(devx)
     ops.check_device_errors()
 
+    # ---- correctness of the sum over ranks (outside every timed region): one row-parallel
+    # output against the fp32 sum of the gathered per-rank partial products
+    tp_check = None
+    if world > 1:
+        lin = layers[0]["down"]
+        prep = lin.local.prepare_input(devx["d_in"])
+        partial = lin.local.apply_prepared(prep).clone()
+        reduced = lin.apply_prepared_reduced(prep).clone()
+        parts = [torch.empty_like(partial) for _ in range(world)]
+        dist.all_gather(parts, partial)
+        want = torch.stack(parts).float().sum(0)
+        rel = float((reduced.float() - want).norm() / want.norm())
+        ops.check_device_errors()
+        flag = torch.tensor([1.0 if (rel <= 5e-3 and bool(torch.isfinite(reduced).all())) else 0.0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if float(flag.item()) != 1.0:
+            raise SystemExit(f"tp_check failed on rank {rank}: all-reduced down_proj output differs from the fp32 sum "
+                             f"of the partial products (relative Frobenius error {rel:.3e})")
+        tp_check = {"status": "ok", "layer": "down_proj of layer 0", "rel_fro_vs_fp32_sum": round(rel, 6), "tolerance": 5e-3}
+        del parts, want, partial, reduced, prep
+
     # The step is launch-bound on the host once the work is split over several GPUs, so it is
     # captured once into a CUDA graph (kernels, memsets and the NCCL all-reduces) and replayed;
     # --no-graph times eager launches instead.
@@ -362,8 +383,8 @@ def run_ours(args):
     roofline = {"bound": "tensor", "kernel": "gemm_kernel<256,sparse+dense> (gate_up)", "achieved": round(achieved, 1),
                 "peak": round(p_dense_fp4, 1), "unit": "TFLOP/s", "frac": round(achieved / p_dense_fp4, 4),
                 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this shape on
-                # one GPU (ncu capture summarised in profiles/gemm_kernel_fused_pair.md); algorithmic bytes
-                # are 195 MB (78 MB of operands, 117 MB of output, part of which is still in L2 at kernel end)
+                # one GPU (one ncu capture); algorithmic bytes are 195 MB (78 MB of operands, 117 MB of
+                # output, part of which is still in L2 at kernel end)
                 "traffic": 158.1e6 if world == 1 and m == 2048 else None,
                 "peak_source": f"4 x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS (dense FP4 = 4 x bf16 rate)",
                 "flops_convention": "3*M*N*K dense-FP4-equivalent (2MNK dense pass + 2MNK sparse pass at 2x rate)",
@@ -457,6 +478,9 @@ def run_ours(args):
         "gpu_launches": args.steps * layers_n * (12 + (2 if world > 1 else 0)),
         "clocks": clocks,
     }
+    if tp_check is not None:
+        result["tp_check"] = tp_check["status"]
+        result["tp_check_detail"] = tp_check
     if breakdown is not None:
         result["kernel_breakdown"] = breakdown
     if rank == 0:

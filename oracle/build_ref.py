@@ -13,6 +13,7 @@ optional: tests that use it skip when it is absent.
 """
 from __future__ import annotations
 
+import os
 import subprocess
 import sys
 from concurrent.futures import ThreadPoolExecutor
@@ -33,7 +34,14 @@ def cutlass_root() -> Path:
     return root
 
 
-def build(ref: Path = Path("/root/reference"), with_gemm: bool = False) -> None:
+def reference_dir() -> Path:
+    """The reference checkout: $SHARQ_REFERENCE_DIR, else a directory named `reference` beside this repository."""
+    env = os.environ.get("SHARQ_REFERENCE_DIR")
+    return Path(env) if env else HERE.parent.parent / "reference"
+
+
+def build(ref: Path = None, with_gemm: bool = False) -> None:
+    ref = reference_dir() if ref is None else Path(ref)
     if not (ref / "kernels" / "src").exists():
         raise SystemExit(f"no reference checkout at {ref}; oracle/_ref not built")
     cut = cutlass_root()
@@ -68,4 +76,4 @@ def build(ref: Path = Path("/root/reference"), with_gemm: bool = False) -> None:
 
 if __name__ == "__main__":
     _args = [a for a in sys.argv[1:] if not a.startswith("--")]
-    build(Path(_args[0]) if _args else Path("/root/reference"), "--gemm" in sys.argv)
+    build(Path(_args[0]) if _args else None, "--gemm" in sys.argv)

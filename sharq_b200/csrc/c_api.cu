@@ -144,6 +144,8 @@ int sharq_rope_inplace(void *x_bf16, int rows, int row_stride, int seq_len, int 
   SHARQ_REQUIRE(row_stride >= heads * head_dim && row_stride % 8 == 0,
                 "row_stride must cover heads * head_dim and be a multiple of 8");
   SHARQ_REQUIRE((reinterpret_cast<uintptr_t>(x_bf16) & 15) == 0, "x must be 16-byte aligned");
+  SHARQ_REQUIRE(((reinterpret_cast<uintptr_t>(cos_bf16) | reinterpret_cast<uintptr_t>(sin_bf16)) & 15) == 0,
+                "cos and sin must be 16-byte aligned");
   return check_cuda(sharq::run_rope_inplace(x_bf16, rows, row_stride, seq_len, heads, head_dim, cos_bf16, sin_bf16,
                                             as_stream(stream)),
                     "rope_inplace");
@@ -153,6 +155,8 @@ int sharq_scatter_add_scaled(void *out_bf16, const void *y_bf16, const int64_t *
                              int width, void *stream) {
   SHARQ_REQUIRE(out_bf16 && y_bf16 && rows && w_bf16, "null buffer");
   SHARQ_REQUIRE(n_rows >= 0 && width > 0 && width % 8 == 0, "n_rows must be >= 0 and width a positive multiple of 8");
+  SHARQ_REQUIRE(((reinterpret_cast<uintptr_t>(out_bf16) | reinterpret_cast<uintptr_t>(y_bf16)) & 15) == 0,
+                "out and y must be 16-byte aligned");
   return check_cuda(sharq::run_scatter_add_scaled(out_bf16, y_bf16, reinterpret_cast<const long long *>(rows), w_bf16,
                                                   n_rows, width, as_stream(stream)),
                     "scatter_add_scaled");
@@ -287,6 +291,8 @@ int sharq_matmul_ws(const void *a, const void *b, const void *sfa, const void *s
   g.error_flag = error_flag;
   g.workspace = workspace;
   g.workspace_bytes = workspace ? workspace_bytes : 0;
+  SHARQ_REQUIRE(workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 15) == 0,
+                "workspace must be 16-byte aligned");
   return check_cuda(sharq::run_gemm(g, as_stream(stream)), "matmul");
 }
 
@@ -318,6 +324,8 @@ int sharq_sparse_matmul_ws(const void *a_comp, const void *b, const void *e, con
   g.error_flag = error_flag;
   g.workspace = workspace;
   g.workspace_bytes = workspace ? workspace_bytes : 0;
+  SHARQ_REQUIRE(workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 15) == 0,
+                "workspace must be 16-byte aligned");
   return check_cuda(sharq::run_gemm(g, as_stream(stream)), "sparse_matmul");
 }
 
@@ -356,6 +364,8 @@ int sharq_linear_gemm_ws(const void *a_comp, const void *e, const void *sfa_spar
   g.error_flag = error_flag;
   g.workspace = workspace;
   g.workspace_bytes = workspace ? workspace_bytes : 0;
+  SHARQ_REQUIRE(workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 15) == 0,
+                "workspace must be 16-byte aligned");
   return check_cuda(sharq::run_gemm(g, as_stream(stream)), "linear_gemm");
 }
 

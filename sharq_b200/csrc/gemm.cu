@@ -45,28 +45,6 @@ namespace {
 constexpr int kBM = 128;
 constexpr int kBK = 256;  // logical K per stage
 constexpr int kEpiWarps = 8;
-// Optional instrumentation build (-DSHARQ_GEMM_TIMING): cycles the producer and MMA threads
-// spend in each wait and issue phase, summed into g_timing and read by
-// sharq_debug_read_timing().  Off in the shipped library.
-#ifdef SHARQ_GEMM_TIMING
-__device__ unsigned long long g_timing[8];
-#define TIMING_T0() long long t0_ = clock64()
-#define TIMING_ADD(slot) do { atomicAdd(&g_timing[slot], (unsigned long long)(clock64() - t0_)); t0_ = clock64(); } while (0)
-// wall-clock (ns) stamps of CTA 0's phases, overwritten by every launch
-__device__ unsigned long long g_stamps[16];
-__device__ __forceinline__ void timing_stamp(int slot) {
-  if (blockIdx.x == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_stamps[slot] = t;
-  }
-}
-#define TIMING_STAMP(slot) timing_stamp(slot)
-#else
-#define TIMING_STAMP(slot) do {} while (0)
-#define TIMING_T0() do {} while (0)
-#define TIMING_ADD(slot) do {} while (0)
-#endif
 constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 
 // Shared-memory stage and tensor-memory column layout.  In pair mode BN is the pair's tile
@@ -235,6 +213,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const bool leader = cta_rank == 0;
   const int k_stages = (p.k + kBK - 1) / kBK;
   const int aligned_m = (p.m + 127) / 128 * 128;
+  const int a_bands = aligned_m / 128;     // 128-row bands of the activation operands
+  const int b_bands = (p.n + 127) / 128;   // 128-row bands of the weight scale factors
   const int tiles_sp = p.k / 128;  // 512-byte scale tiles per 128-row band, 32-group layout
   const int tiles_d = p.k / 64;    // same, 16-group layout
   // work units: a unit is one output tile of a CTA (128 x BN) or of a pair (256 x BN)
@@ -255,7 +235,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     if (SPARSE) ptx::tma_prefetch_desc(&tm_a_comp);
   }
   if (threadIdx.x == 0) {
-    TIMING_STAMP(0);
     for (int s = 0; s < S; ++s) {
       ptx::mbar_init(full_bar + s, 1);
       ptx::mbar_init(empty_bar + s, 1);
@@ -275,7 +254,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (PAIR) ptx::cluster_sync();  // both CTAs' barriers exist before any remote arrive
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) TIMING_STAMP(1);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -287,17 +265,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const int m_tile = PAIR ? 2 * (tile % m_units) + (int)cta_rank : (tile % m_units);
         const int n_tile = tile / m_units;
         const int w_row = n_tile * BN + (PAIR ? (int)cta_rank * (BN / 2) : 0);
+        // The metadata and scale-factor copies are plain bulk copies without bounds checks.  A
+        // tile may hang over the last 128-row band (the second CTA of a pair when ceil(M/128) is
+        // odd, the second weight band of a 256-wide tile when ceil(N/128) is odd): such a band
+        // is loaded from the last band that exists.  Its rows / columns are masked on output.
+        const int a_band = min(m_tile, a_bands - 1);
+        int b_band[L::kBands];
+#pragma unroll
+        for (int b = 0; b < L::kBands; ++b) b_band[b] = min(n_tile * L::kBands + b, b_bands - 1);
         for (int it = k_begin(u), it_end = k_end(u); it < it_end; ++it, ++g) {
           const int s = (int)(g % S);
           const uint32_t ph = (g / S) & 1u;
-          TIMING_T0();
           if (!ptx::mbar_wait(empty_bar + s, ph ^ 1u, abort_flag)) {
             *abort_flag = 1;
             atomicExch(p.error_flag, 1);
             ok = false;
             break;
           }
-          TIMING_ADD(0);
           uint8_t *st = smem + s * L::kStageBytes;
           const int n_sp = SPARSE ? min(2, tiles_sp - 2 * it) : 0;
           const int n_d = DENSE ? min(4, tiles_d - 4 * it) : 0;
@@ -307,28 +291,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           ptx::tma_load_2d(st + L::kOffW, &tm_w, it * 128, w_row, full_bar + s);
           if (DENSE) {
             ptx::tma_load_2d(st + L::kOffADense, &tm_a_dense, it * 128, m_tile * kBM, full_bar + s);
-            ptx::bulk_load_1d(st + L::kOffSfaD, p.sfa_dense + ((size_t)m_tile * tiles_d + 4 * (size_t)it) * 512,
+            ptx::bulk_load_1d(st + L::kOffSfaD, p.sfa_dense + ((size_t)a_band * tiles_d + 4 * (size_t)it) * 512,
                               (uint32_t)n_d * 512, full_bar + s);
 #pragma unroll
             for (int b = 0; b < L::kBands; ++b)
               ptx::bulk_load_1d(st + L::kOffSfbD + b * 2048,
-                                p.sfb_dense + ((size_t)(n_tile * L::kBands + b) * tiles_d + 4 * (size_t)it) * 512,
+                                p.sfb_dense + ((size_t)b_band[b] * tiles_d + 4 * (size_t)it) * 512,
                                 (uint32_t)n_d * 512, full_bar + s);
           }
           if (SPARSE) {
             ptx::tma_load_2d(st + L::kOffAComp, &tm_a_comp, it * 64, m_tile * kBM, full_bar + s);
-            ptx::bulk_load_1d(st + L::kOffE, p.e + ((size_t)it * aligned_m + (size_t)m_tile * 128) * 16, 2048,
+            ptx::bulk_load_1d(st + L::kOffE, p.e + ((size_t)it * aligned_m + (size_t)a_band * 128) * 16, 2048,
                               full_bar + s);
-            ptx::bulk_load_1d(st + L::kOffSfaSp, p.sfa_sparse + ((size_t)m_tile * tiles_sp + 2 * (size_t)it) * 512,
+            ptx::bulk_load_1d(st + L::kOffSfaSp, p.sfa_sparse + ((size_t)a_band * tiles_sp + 2 * (size_t)it) * 512,
                               (uint32_t)n_sp * 512, full_bar + s);
 #pragma unroll
             for (int b = 0; b < L::kBands; ++b)
               ptx::bulk_load_1d(st + L::kOffSfbSp + b * 1024,
-                                p.sfb_sparse + ((size_t)(n_tile * L::kBands + b) * tiles_sp + 2 * (size_t)it) * 512,
+                                p.sfb_sparse + ((size_t)b_band[b] * tiles_sp + 2 * (size_t)it) * 512,
                                 (uint32_t)n_sp * 512, full_bar + s);
           }
-          TIMING_ADD(1);
-          if (g == 0) TIMING_STAMP(2);
         }
       }
     }
@@ -359,10 +341,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         bool ok = true;
         for (int u = unit0; u < num_units && ok; u += unit_stride, ++tile_iter) {
           // the epilogue warps must have pulled the previous tile out of tensor memory
-          TIMING_T0();
           const bool drained = PAIR ? ptx::mbar_wait_cluster(acc_empty_bar, (tile_iter & 1u) ^ 1u, abort_flag)
                                     : ptx::mbar_wait(acc_empty_bar, (tile_iter & 1u) ^ 1u, abort_flag);
-          TIMING_ADD(5);
           if (!drained) {
             *abort_flag = 1;
             atomicExch(p.error_flag, 5);
@@ -373,11 +353,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           for (int it = k_begin(u), it_end = k_end(u); it < it_end; ++it, ++g) {
             const int s = (int)(g % S);
             const uint32_t ph = (g / S) & 1u;
-            TIMING_T0();
             bool got = ptx::mbar_wait(full_bar + s, ph, abort_flag);
-            TIMING_ADD(2);
             if (PAIR && got) got = ptx::mbar_wait_cluster(peer_bar + s, ph, abort_flag);
-            TIMING_ADD(3);
             if (!got) {
               *abort_flag = 1;
               atomicExch(p.error_flag, 2);
@@ -385,7 +362,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               break;
             }
             ptx::tc_fence_after();
-            if (g == 0) TIMING_STAMP(3);
             const uint32_t st = ptx::smem_u32(smem + s * L::kStageBytes);
             const int n_sp = SPARSE ? min(2, tiles_sp - 2 * it) : 0;
             const int n_d = DENSE ? min(4, tiles_d - 4 * it) : 0;
@@ -449,14 +425,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               ptx::tc_commit_multicast2(empty_bar + s, 3);
             else
               ptx::tc_commit<1>(empty_bar + s);
-            TIMING_ADD(4);
           }
           if (ok) {
             if (PAIR)
               ptx::tc_commit_multicast2(acc_full_bar, 3);
             else
               ptx::tc_commit<1>(acc_full_bar);
-            TIMING_STAMP(4);
           }
         }
       }
@@ -488,14 +462,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after();
-      if (warp == 2 && lane == 0) TIMING_STAMP(5);
       uint32_t acc[kColsPerEpiWarp];
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(L::kColAcc + half * kColsPerEpiWarp);
 #pragma unroll
       for (int c = 0; c < kColsPerEpiWarp / 32; ++c)
         ptx::tmem_ld_32x32b_x32(taddr + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&acc[32 * c]));
       ptx::tmem_ld_wait();
-      if (warp == 2 && lane == 0) TIMING_STAMP(8);
       // the accumulator is in registers: give tensor memory back before the slow part
       ptx::tc_fence_before();
       __syncwarp();
@@ -542,14 +514,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               *reinterpret_cast<uint4 *>(p.d + (size_t)(row0 + r) * p.n + gcol) = v;
           }
           __syncwarp();
-          if (warp == 2 && lane == 0) TIMING_STAMP(9 + c);
         }
       } else {
 #pragma unroll
         for (int c = 0; c < kColsPerEpiWarp / 32; ++c)
           epilogue_chunk(p, &acc[32 * c], row, col_base + 32 * c, alpha, beta, has_c);
       }
-      if (warp == 2 && lane == 0) TIMING_STAMP(6);
     }
   }
 
@@ -560,7 +530,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     ptx::tc_fence_after();
     ptx::tmem_dealloc<CG>(tmem_base, L::kTmemCols);
   }
-  if (threadIdx.x == 0) TIMING_STAMP(7);
 }
 
 // Second kernel of a split-K GEMM: the epilogue on the accumulated fp32 sums, 32 columns per thread.
@@ -736,21 +705,6 @@ cudaError_t launch(const GemmArgs &a, cudaStream_t stream) {
 }
 
 }  // namespace
-
-#ifdef SHARQ_GEMM_TIMING
-extern "C" int sharq_debug_read_stamps(unsigned long long *out) {
-  return cudaMemcpyFromSymbol(out, g_stamps, sizeof(g_stamps)) == cudaSuccess ? 0 : 1;
-}
-
-extern "C" int sharq_debug_read_timing(unsigned long long *out, int reset) {
-  if (cudaMemcpyFromSymbol(out, g_timing, sizeof(g_timing)) != cudaSuccess) return 1;
-  if (reset) {
-    unsigned long long z[8] = {};
-    if (cudaMemcpyToSymbol(g_timing, z, sizeof(z)) != cudaSuccess) return 1;
-  }
-  return 0;
-}
-#endif
 
 cudaError_t run_gemm(const GemmArgs &a, cudaStream_t stream) {
   const bool sparse = a.a_comp != nullptr;

@@ -491,6 +491,13 @@ def sharq_linear_gemm(A_comp, E, SFA_sparse, Q_res, SF_res, QW, SFW_sparse, SFW_
     M, K = int(Q_res.shape[0]), int(Q_res.shape[1]) * 2
     N = int(QW.shape[0])
     dev = Q_res.device
+    ea, ee, esf, eq, _ = get_fused_sparse_residual_buffer_sizes(M, N, K)
+    for t, want, nm in ((A_comp, ea, "A_comp"), (E, ee, "E"), (SFA_sparse, esf, "SFA_sparse"), (Q_res, eq, "Q_res"),
+                        (SF_res, esf, "SF_res"), (QW, N * (K // 2), "QW"), (SFW_sparse, _sf_bytes(N, K), "SFW_sparse"),
+                        (SFW_dense, _sf_bytes(N, K), "SFW_dense")):
+        _check(t.is_cuda and t.device == dev and t.dtype == torch.uint8 and t.is_contiguous(),
+               f"{nm} must be a contiguous CUDA uint8 tensor on the device of Q_res")
+        _check(t.numel() == want, f"{nm}.numel() mismatch: expected {want}, got {t.numel()}")
     if bias is not None:
         _check(bias.is_cuda and bias.dtype == torch.bfloat16 and bias.numel() == N and bias.is_contiguous(),
                "bias must be a contiguous CUDA bfloat16 tensor with N elements")

@@ -85,6 +85,11 @@ class QLinearLayer(nn.Module):
             self.bias = None
         return self
 
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+        # the fused GEMM takes the weight tensor scale as a host scalar: keep it in step with the buffer
+        self.weight_scale_host = float(self.weight_scale.item())
+
     @torch.no_grad()
     def prepare_input(self, x_2d: torch.Tensor, out_features_hint: Optional[int] = None):
         x_2d = x_2d.to(torch.bfloat16)

@@ -179,14 +179,27 @@ def sum_buffer(group, device: torch.device, nbytes: int) -> Optional[SymmetricSu
             return None
         if torch.cuda.is_current_stream_capturing():
             raise RuntimeError("the symmetric sum buffer must be created before stream capture: run the layer once first")
+        err = None
         try:
             buf = SymmetricSumBuffer(nbytes, group, device)
-        except RuntimeError:
+        except RuntimeError as exc:
+            buf, err = None, exc
+        # every rank must take the same path: one that failed while the others succeeded would
+        # issue a different collective from theirs.  Agree on the outcome before caching it.
+        ok = torch.tensor([0 if buf is None else 1], dtype=torch.int32, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if int(ok.item()) == 0:
+            buf = None  # no multicast on (some rank of) this system: torch.distributed's all_reduce is used
             if os.environ.get("SHARQ_TP_ALLREDUCE", "auto").lower() == "multimem":
-                raise
-            buf = None  # no multicast on this system: torch.distributed's all_reduce is used
+                raise RuntimeError(f"SHARQ_TP_ALLREDUCE=multimem but the symmetric buffer could not be set up: {err}")
         _SUM_BUFFERS[key] = buf
     return buf
+
+
+def reserve_sum_buffer(group, device: torch.device, nbytes: int) -> Optional[SymmetricSumBuffer]:
+    """Create the group's shared buffer once, sized for the largest row-parallel output of the
+    model (M x N x 2 bytes), so that no forward pass has to grow it (growth is a collective)."""
+    return sum_buffer(group, device, nbytes)
 
 
 def release_sum_buffers() -> None:

@@ -42,7 +42,10 @@ def make_inputs(m, k, n, seed):
 
 
 def main() -> None:
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    import os
+
+    default = os.environ.get("SHARQ_REFERENCE_DIR") or str(Path(__file__).resolve().parents[3] / "reference")
+    ref = Path(sys.argv[1] if len(sys.argv) > 1 else default)
     sys.path.insert(0, str(ref / "model"))
     from qLinearLayer import QLinearLayer  # noqa: E402  (the reference's own module)
     import quantize as refq  # noqa: E402

@@ -1,0 +1,62 @@
+"""The GEMM producer's bulk copies stay inside the operand buffers.
+
+The metadata and scale-factor tiles are fetched with plain bulk copies that have no bounds
+check, so their offsets are restated here exactly as the producer warp of
+sharq_b200/csrc/gemm.cu computes them and compared, over a grid of shapes and kernel variants
+(single-CTA 128/256-wide tiles, CTA pairs), with the buffer sizes the C ABI reports
+(sharq_get_sparse_nvfp4_buffer_sizes / sharq_get_fused_sparse_residual_buffer_sizes).
+"""
+import ctypes
+import itertools
+
+import pytest
+
+from sharq_b200 import _lib
+
+
+def _sizes(m, n, k):
+    lib = _lib.lib()
+    sp = (ctypes.c_int64 * 4)()
+    assert lib.sharq_get_sparse_nvfp4_buffer_sizes(m, n, k, sp) == 0
+    fu = (ctypes.c_int64 * 5)()
+    assert lib.sharq_get_fused_sparse_residual_buffer_sizes(m, n, k, fu) == 0
+    return {"a_comp": sp[0], "e": sp[1], "sfa": sp[2], "sfb": sp[3], "q_res": fu[3], "sf_res": fu[4]}
+
+
+def _producer_reads(m, n, k, bn, pair):
+    """Yield (buffer, offset, nbytes) of every plain bulk copy of one GEMM launch."""
+    bands = bn // 128
+    k_stages = (k + 255) // 256
+    aligned_m = (m + 127) // 128 * 128
+    a_bands, b_bands = aligned_m // 128, (n + 127) // 128
+    tiles_sp, tiles_d = k // 128, k // 64
+    m_units = (m + 255) // 256 if pair else (m + 127) // 128
+    n_tiles = (n + bn - 1) // bn
+    for tile in range(m_units * n_tiles):
+        for cta_rank in ((0, 1) if pair else (0,)):
+            m_tile = 2 * (tile % m_units) + cta_rank if pair else tile % m_units
+            n_tile = tile // m_units
+            a_band = min(m_tile, a_bands - 1)
+            b_band = [min(n_tile * bands + b, b_bands - 1) for b in range(bands)]
+            for it in range(k_stages):
+                n_sp = min(2, tiles_sp - 2 * it)
+                n_d = min(4, tiles_d - 4 * it)
+                yield "sf_res", (a_band * tiles_d + 4 * it) * 512, n_d * 512
+                yield "e", (it * aligned_m + a_band * 128) * 16, 2048
+                yield "sfa", (a_band * tiles_sp + 2 * it) * 512, n_sp * 512
+                for b in range(bands):
+                    yield "sfb", (b_band[b] * tiles_d + 4 * it) * 512, n_d * 512
+                    yield "sfb", (b_band[b] * tiles_sp + 2 * it) * 512, n_sp * 512
+
+
+M_CASES = (1, 16, 127, 128, 129, 256, 257, 300, 384, 2100, 2176)
+N_CASES = (8, 128, 200, 256, 300, 384, 640, 4096)
+K_CASES = (128, 256, 384, 896, 4096)
+
+
+@pytest.mark.parametrize("bn,pair", [(128, False), (256, False), (256, True)])
+def test_bulk_copies_stay_inside_the_buffers(bn, pair):
+    for m, n, k in itertools.product(M_CASES, N_CASES, K_CASES):
+        size = _sizes(m, n, k)
+        for name, off, nbytes in _producer_reads(m, n, k, bn, pair):
+            assert off >= 0 and off + nbytes <= size[name], (name, m, n, k, bn, pair, off, nbytes, size[name])

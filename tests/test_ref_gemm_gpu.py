@@ -9,9 +9,8 @@ must be bit-identical to the reference; the single-launch fused GEMM rounds to b
 instead of twice and must stay within the GEMM tolerance of the reference result.  The
 tests skip when the library has not been built.
 
-With SHARQ_REF_GEMM_TIMING=1 the timing test prints one line per shape (run with -s)."""
+The timing test asserts with few iterations and prints one line per shape (run with -s)."""
 import ctypes
-import os
 from pathlib import Path
 
 import pytest
@@ -76,7 +75,8 @@ class Case:
              dptr(self.err), stream_ptr())
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 256, 512), (300, 384, 1024), (2048, 4096, 4096), (1024, 6144, 4096)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 512), (300, 384, 1024), (2048, 4096, 4096), (1024, 6144, 4096),
+                                   (2048, 28672, 4096), (8192, 4096, 14336), (2100, 4096, 4096)])
 def test_gemms_equal_reference_cutlass(ref, m, n, k):
     c = Case(m, n, k)
     ys, yd, ms, md = c.out
@@ -113,22 +113,32 @@ def _time_us(fn, iters=30):
     return e0.elapsed_time(e1) / iters * 1e3
 
 
-@pytest.mark.skipif(os.environ.get("SHARQ_REF_GEMM_TIMING") != "1", reason="set SHARQ_REF_GEMM_TIMING=1 to time")
-def test_time_against_reference_cutlass(ref):
-    shapes = {"o_proj": (4096, 4096), "qkv_proj": (6144, 4096), "down_proj": (4096, 14336), "gate_up_proj": (28672, 4096)}
+STANDALONE_SLACK = 1.6  # stand-alone dense / sparse GEMM time allowed relative to the reference's CUTLASS kernels
+SHAPES_M2048 = {"o_proj": (4096, 4096), "qkv_proj": (6144, 4096), "down_proj": (4096, 14336), "gate_up_proj": (28672, 4096)}
+
+
+@pytest.mark.parametrize("name", list(SHAPES_M2048))
+def test_fused_launch_beats_reference_pair(ref, name):
+    """The single fused launch must be faster than the reference's sparse + dense(beta = 1) pair
+    on the same device and buffers at the Llama-3-8B projection shapes, M = 2048; the
+    stand-alone dense and sparse variants must stay within STANDALONE_SLACK of the reference kernels.
+    Few iterations: this is an assertion, not a benchmark.  One line per shape with -s."""
+    n, k = SHAPES_M2048[name]
     m = 2048
     with torch.cuda.stream(torch.cuda.default_stream()):
-        for name, (n, k) in shapes.items():
-            c = Case(m, n, k)
-            ys, yd, ms, md = c.out
-            t = {
-                "ref_sparse": _time_us(lambda: c.ref_sparse(ref, ys)),
-                "ref_dense_beta1": _time_us(lambda: c.ref_dense(ref, ys, yd, 1.0)),
-                "my_sparse": _time_us(lambda: c.my_sparse(ms)),
-                "my_dense_beta1": _time_us(lambda: c.my_dense(ms, md, 1.0)),
-                "my_fused": _time_us(lambda: c.my_fused(md)),
-            }
-            pair = t["ref_sparse"] + t["ref_dense_beta1"]
-            print(f"\n{name} M={m} N={n} K={k} us: " + " ".join(f"{k_}={v:.1f}" for k_, v in t.items())
-                  + f" | reference pair {pair:.1f} -> fused is {pair / t['my_fused']:.2f}x", flush=True)
-            assert int(c.err.item()) == 0
+        c = Case(m, n, k)
+        ys, yd, ms, md = c.out
+        t = {
+            "ref_sparse": _time_us(lambda: c.ref_sparse(ref, ys), 10),
+            "ref_dense_beta1": _time_us(lambda: c.ref_dense(ref, ys, yd, 1.0), 10),
+            "my_sparse": _time_us(lambda: c.my_sparse(ms), 10),
+            "my_dense_beta1": _time_us(lambda: c.my_dense(ms, md, 1.0), 10),
+            "my_fused": _time_us(lambda: c.my_fused(md), 10),
+        }
+    pair = t["ref_sparse"] + t["ref_dense_beta1"]
+    print(f"\n{name} M={m} N={n} K={k} us: " + " ".join(f"{k_}={v:.1f}" for k_, v in t.items())
+          + f" | reference pair {pair:.1f} -> fused is {pair / t['my_fused']:.2f}x", flush=True)
+    assert int(c.err.item()) == 0
+    assert t["my_fused"] < pair, t
+    assert t["my_sparse"] <= STANDALONE_SLACK * t["ref_sparse"], t
+    assert t["my_dense_beta1"] <= STANDALONE_SLACK * t["ref_dense_beta1"], t
