@@ -27,6 +27,8 @@
 #include "common.cuh"
 #include "prepare.cuh"
 
+#include <cstdlib>
+
 namespace sharq {
 
 namespace {
@@ -325,6 +327,29 @@ __device__ __forceinline__ uint32_t scaled_bf16x2(float ya, float yb, float scal
   return pack_bf16x2(qa, qb);
 }
 
+// The same for a whole 32-element group with the boundary test done on packed halves: the low
+// 16 bits of both products of a word go into one register (one byte permute), 0x8004 is added
+// to each half (a carry out of the low half can only raise the high half by one, which the
+// wider threshold absorbs), and a packed unsigned minimum over the group is compared once.
+// A group in which any product lies within the window is redone with IEEE divisions.
+__device__ __forceinline__ void scale_group32(uint32_t (&w)[16], float scale, float recip) {
+  uint32_t out[16];
+  uint32_t nearest = 0xFFFFFFFFu;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float qa = __fmul_rn(lo_f(w[i]), recip), qb = __fmul_rn(hi_f(w[i]), recip);
+    const uint32_t lows = __byte_perm(__float_as_uint(qa), __float_as_uint(qb), 0x5410);
+    nearest = __vminu2(nearest, lows + 0x80048004u);
+    out[i] = pack_bf16x2(qa, qb);
+  }
+  if ((nearest & 0xFFFFu) < 10u || (nearest >> 16) < 10u) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) out[i] = pack_bf16x2(__fdiv_rn(lo_f(w[i]), scale), __fdiv_rn(hi_f(w[i]), scale));
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) w[i] = out[i];
+}
+
 // ---------------------------------------------------------------------------
 // Prepare kernel.
 //   kMode 0: input already scaled (drop-in for fused_sparse_residual_quantize_x)
@@ -538,6 +563,327 @@ __global__ void __launch_bounds__(kPrepareThreads, kPrepareCtasPerSm) prepare_ke
   }
 }
 
+
+// ---------------------------------------------------------------------------
+// One-launch scaled prepare (modes 1 and 2 with their statistics pass folded in).
+//
+// A cooperative grid of one CTA per SM; CTA b owns a contiguous block of rows.  Phase 1: the
+// CTA streams its rows through shared memory in chunks, computes the row statistics of the
+// RMSNorm path in the reference's summation order (group sums as FMA chains, then left to
+// right over the groups by one thread per row), replaces the cached rows by the normalised
+// bf16 values and folds max|y| into the tensor absmax word.  All CTAs then meet at a
+// grid-wide barrier (a counter in the caller's workspace, bounded spin), read the absmax and
+// quantise: the last chunk straight from shared memory, earlier chunks (when the CTA's rows
+// do not fit) from a second read of the input.  At 2048 x 4096 every row stays on chip, so
+// the input is read from HBM exactly once and the statistics cost no launch of their own.
+// ---------------------------------------------------------------------------
+constexpr int kFusedThreads = 512;
+constexpr int kFusedWarps = kFusedThreads / 32;
+constexpr int kFusedSmemBudget = 200 * 1024;       // dynamic shared memory the row cache may use
+constexpr long long kGridBarrierLimitCycles = 2000000000LL;  // about one second
+
+__device__ int g_prepare_timeouts = 0;  // grid barriers that ran out (the result of such a call is wrong)
+
+struct FusedParams {
+  const __nv_bfloat16 *x;
+  const __nv_bfloat16 *residual;  // kAdd: the input is bf16(x + residual) ...
+  __nv_bfloat16 *sum_out;         // ... which is also written here
+  const __nv_bfloat16 *gamma;
+  float eps;
+  float *inv_rms;            // [m], mode 1
+  unsigned int *amax_bits;   // zero on entry
+  unsigned int *arrive;      // zero on entry: grid barrier counter
+  float *scale_out;
+  uint8_t *a_comp, *e, *sfa_sparse, *q_res, *sf_res;
+  int m, k;
+  int rows_per_cta;
+  int chunk_rows;  // rows of one shared-memory chunk
+};
+
+// uint4 index of 16-byte piece j of group g inside a cached row: the pieces of a group are
+// permuted so that a quarter-warp reading or writing neighbouring groups hits distinct banks
+__device__ __forceinline__ int cache_slot(int g, int j) { return (g << 2) + (j ^ ((g >> 1) & 3)); }
+
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int *p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// stores of one quantised group: payloads by the owner lane, metadata and scale factors
+// combined over neighbouring lanes (groups g, g+1[, g+2, g+3] of the same row)
+__device__ __forceinline__ void store_group(const FusedParams &p, const GroupOut &o, int row, int group, bool live,
+                                            bool in_padded, int aligned_m, int lane) {
+  const int k = p.k, groups32 = k >> 5;
+  if (live) {
+    *reinterpret_cast<uint4 *>(p.q_res + (size_t)row * (k / 2) + (size_t)group * 16) =
+        make_uint4(o.q_res[0], o.q_res[1], o.q_res[2], o.q_res[3]);
+    *reinterpret_cast<uint2 *>(p.a_comp + (size_t)row * (k / 4) + (size_t)group * 8) = make_uint2(o.a_comp[0], o.a_comp[1]);
+  }
+  const uint32_t mine = o.meta & 0xFFFFu;
+  const uint32_t other = __shfl_down_sync(0xffffffffu, mine, 1);
+  if ((lane & 1) == 0 && in_padded)
+    *reinterpret_cast<uint32_t *>(p.e + (size_t)(group >> 3) * aligned_m * 16 + (size_t)row * 16 + (size_t)(group & 7) * 2) =
+        mine | (other << 16);
+  const uint32_t sv = o.sf_sparse;
+  const uint32_t s1 = __shfl_down_sync(0xffffffffu, sv, 1);
+  const uint32_t s2 = __shfl_down_sync(0xffffffffu, sv, 2);
+  const uint32_t s3 = __shfl_down_sync(0xffffffffu, sv, 3);
+  const uint32_t r2 = o.sf_res;
+  const uint32_t r2n = __shfl_down_sync(0xffffffffu, r2, 1);
+  if (live) {
+    if ((lane & 3) == 0)
+      *reinterpret_cast<uint32_t *>(p.sfa_sparse + sf_offset(row, group, groups32)) = sv | (s1 << 8) | (s2 << 16) | (s3 << 24);
+    if ((lane & 1) == 0) *reinterpret_cast<uint32_t *>(p.sf_res + sf_offset(row, 2 * group, k / 16)) = r2 | (r2n << 16);
+  }
+}
+
+template <int kMode, bool kAdd>
+__global__ void __launch_bounds__(kFusedThreads, 1) prepare_fused_kernel(const FusedParams p) {
+  static_assert(kMode == 1 || kMode == 2, "modes with a statistics pass");
+  const int m = p.m, k = p.k;
+  const int groups32 = k >> 5;
+  const int groups_padded = ((k + 255) / 256) * 8;  // groups of the metadata tiles (256 columns each)
+  const int aligned_m = (m + 127) / 128 * 128;
+  const int row_vecs = k >> 3;                     // uint4 per row
+  const int partial_stride = groups32 + 1;         // padded: the row sums of different rows hit different banks
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  __shared__ ScaleTables tbl;
+  __shared__ float warp_red[kFusedWarps];
+  __shared__ int barrier_ok;
+  extern __shared__ uint4 fused_smem[];
+  uint4 *gamma_s = fused_smem;                                      // mode 1: k bf16, pieces permuted like the cache
+  uint4 *cache = fused_smem + (kMode == 1 ? row_vecs : 0);          // chunk_rows x k bf16
+  float *partial = reinterpret_cast<float *>(cache + (size_t)p.chunk_rows * row_vecs);  // mode 1: chunk_rows x partial_stride
+  float *inv_s = partial + (kMode == 1 ? p.chunk_rows * partial_stride : 0);            // mode 1: rows_per_cta
+
+  if (threadIdx.x < 128) {
+    const float v = ue4m3_to_float(threadIdx.x);
+    tbl.value[threadIdx.x] = v;
+    tbl.recip[threadIdx.x] = __frcp_rn(v);  // code 0 is never looked up (scales are clamped to >= 2^-9)
+  }
+  if (kMode == 1) {
+    const uint4 *gsrc = reinterpret_cast<const uint4 *>(p.gamma);
+    for (int i = threadIdx.x; i < row_vecs; i += kFusedThreads) gamma_s[cache_slot(i >> 2, i & 3)] = __ldg(gsrc + i);
+  }
+
+  // ---- zero what no owner thread writes: padding rows of the metadata and scale-factor
+  // bands, the spare band of the scale buffers, the tail of A_comp
+  {
+    const int worker = blockIdx.x * kFusedThreads + threadIdx.x;
+    const int workers = gridDim.x * kFusedThreads;
+    const size_t bands = (size_t)aligned_m / 128;
+    zero_range(p.sfa_sparse, bands * (size_t)(groups32 / 4) * 512, sf_alloc_bytes(m, k), worker, workers);
+    zero_range(p.sf_res, bands * (size_t)(k / 16 / 4) * 512, sf_alloc_bytes(m, k), worker, workers);
+    zero_range(p.a_comp, (size_t)m * (k / 4), a_comp_bytes(m, k), worker, workers);
+    const int pad_rows = aligned_m - m;
+    const int k_tiles = groups_padded >> 3;
+    const int w_sp = groups32 >> 2, w_res = k >> 6;  // 32-bit scale words per row
+    const int per_row = k_tiles * 4 + w_sp + w_res;  // 32-bit words to clear per padding row
+    for (long long i = worker; i < (long long)pad_rows * per_row; i += workers) {
+      const int row = m + (int)(i / per_row);
+      int j = (int)(i % per_row);
+      if (j < k_tiles * 4) {
+        *reinterpret_cast<uint32_t *>(p.e + ((size_t)(j >> 2) * aligned_m + row) * 16 + (size_t)(j & 3) * 4) = 0u;
+      } else if ((j -= k_tiles * 4) < w_sp) {
+        *reinterpret_cast<uint32_t *>(p.sfa_sparse + sf_offset(row, 4 * j, groups32)) = 0u;
+      } else {
+        j -= w_sp;
+        *reinterpret_cast<uint32_t *>(p.sf_res + sf_offset(row, 4 * j, k / 16)) = 0u;
+      }
+    }
+  }
+
+  const int row_begin = min(m, (int)blockIdx.x * p.rows_per_cta);
+  const int row_end = min(m, row_begin + p.rows_per_cta);
+  const int rows = row_end - row_begin;
+  const int chunks = rows > 0 ? (rows + p.chunk_rows - 1) / p.chunk_rows : 0;
+  const int first_chunk_rows = rows - (chunks - 1) * p.chunk_rows;  // the short chunk goes first, the cached (last) one is full
+  auto chunk_first_row = [&](int c) { return c == 0 ? 0 : first_chunk_rows + (c - 1) * p.chunk_rows; };
+  auto chunk_size = [&](int c) { return c == 0 ? first_chunk_rows : p.chunk_rows; };
+  const __nv_bfloat16 *src = kAdd ? p.sum_out : p.x;  // what a second read of the (summed) input reads
+  __syncthreads();
+
+  // ------------------------------------------------------------------ phase 1: statistics
+  __nv_bfloat162 m2 = __floats2bfloat162_rn(0.0f, 0.0f);
+  for (int c = 0; c < chunks; ++c) {
+    const int c_rows = chunk_size(c), c_row0 = row_begin + chunk_first_row(c);
+    if (c > 0) __syncthreads();  // the previous chunk's cache and partial sums are no longer read
+    for (int t = threadIdx.x; t < c_rows * groups32; t += kFusedThreads) {
+      const int rl = t / groups32, g = t - rl * groups32;
+      const size_t off = (size_t)(c_row0 + rl) * k + (size_t)g * 32;
+      const uint4 *xs = reinterpret_cast<const uint4 *>(p.x + off);
+      uint32_t w[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 v = __ldg(xs + j);
+        w[4 * j + 0] = v.x;
+        w[4 * j + 1] = v.y;
+        w[4 * j + 2] = v.z;
+        w[4 * j + 3] = v.w;
+      }
+      if (kAdd) {
+        const uint4 *rs = reinterpret_cast<const uint4 *>(p.residual + off);
+        uint4 *dst = reinterpret_cast<uint4 *>(p.sum_out + off);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint4 r = __ldg(rs + j);
+          const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            w[4 * j + q] = pack_bf16x2(__fadd_rn(lo_f(w[4 * j + q]), lo_f(rw[q])), __fadd_rn(hi_f(w[4 * j + q]), hi_f(rw[q])));
+          dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        }
+      }
+      uint4 *row_cache = cache + (size_t)rl * row_vecs;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) row_cache[cache_slot(g, j)] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+      if (kMode == 1) {
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float a = lo_f(w[i]), b = hi_f(w[i]);
+          s = __fmaf_rn(a, a, s);  // a*a is exact in float, so this equals s + a*a
+          s = __fmaf_rn(b, b, s);
+        }
+        partial[rl * partial_stride + g] = s;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) m2 = __hmax2(m2, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[i])));
+      }
+    }
+    if (kMode == 1) {
+      __syncthreads();
+      if (threadIdx.x < c_rows) {
+        const float *pr = partial + threadIdx.x * partial_stride;
+        float total = 0.0f;
+        for (int i = 0; i < groups32; ++i) total = __fadd_rn(total, pr[i]);
+        const float inv = rsqrtf(__fadd_rn(__fdiv_rn(total, (float)k), p.eps));
+        inv_s[chunk_first_row(c) + threadIdx.x] = inv;
+        p.inv_rms[c_row0 + threadIdx.x] = inv;
+      }
+      __syncthreads();
+      // normalise in place: the cache then holds y = bf16(x * inv_rms * gamma)
+      for (int t = threadIdx.x; t < c_rows * groups32; t += kFusedThreads) {
+        const int rl = t / groups32, g = t - rl * groups32;
+        const float inv = inv_s[chunk_first_row(c) + rl];
+        uint4 *row_cache = cache + (size_t)rl * row_vecs;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int slot = cache_slot(g, j);
+          const uint4 xv = row_cache[slot];
+          const uint4 gv = gamma_s[slot];
+          const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w}, gw[4] = {gv.x, gv.y, gv.z, gv.w};
+          uint32_t y[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            y[q] = pack_bf16x2(__fmul_rn(__fmul_rn(lo_f(xw[q]), inv), lo_f(gw[q])),
+                               __fmul_rn(__fmul_rn(hi_f(xw[q]), inv), hi_f(gw[q])));
+            m2 = __hmax2(m2, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&y[q])));
+          }
+          row_cache[slot] = make_uint4(y[0], y[1], y[2], y[3]);
+        }
+      }
+    }
+  }
+
+  // ---- CTA absmax -> tensor absmax, grid barrier, tensor scale
+  {
+    float mx = fmaxf(__bfloat162float(m2.x), __bfloat162float(m2.y));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) warp_red[warp] = mx;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+#pragma unroll
+      for (int w = 1; w < kFusedWarps; ++w) mx = fmaxf(mx, warp_red[w]);
+      if (mx > 0.0f) atomicMax(p.amax_bits, __float_as_uint(mx));
+      __threadfence();
+      atomicAdd(p.arrive, 1u);
+      int ok = 1;
+      const long long t0 = clock64();
+      while (ld_acquire_gpu(p.arrive) < gridDim.x) {
+        if (clock64() - t0 > kGridBarrierLimitCycles) {
+          ok = 0;
+          atomicAdd(&g_prepare_timeouts, 1);
+          break;
+        }
+      }
+      barrier_ok = ok;
+    }
+    __syncthreads();
+  }
+  const float amax = __uint_as_float(ld_acquire_gpu(p.amax_bits));
+  // ATen divides a CUDA tensor by a host scalar by multiplying with the float
+  // reciprocal; clamp(min=1e-9) follows (kernels/src/bindings.cpp:337 of the reference).
+  const float scale = fmaxf(__fmul_rn(amax, 1.0f / 2688.0f), 1.0e-9f);
+  const float recip = __frcp_rn(scale);
+  if (p.scale_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *p.scale_out = scale;
+
+  // ------------------------------------------------------------------ phase 2: quantise
+  const int tasks_per_row = (groups_padded + 31) >> 5;  // a warp takes 32 neighbouring groups of one row
+  for (int c = chunks - 1; c >= 0; --c) {
+    const bool cached = c == chunks - 1;
+    const int c_rows = chunk_size(c), c_row0 = row_begin + chunk_first_row(c);
+    for (int wt = warp; wt < c_rows * tasks_per_row; wt += kFusedWarps) {
+      const int rl = wt / tasks_per_row;
+      const int group = (wt - rl * tasks_per_row) * 32 + lane;
+      const int row = c_row0 + rl;
+      const bool live = group < groups32;
+      uint32_t xw[16];
+      GroupOut o;
+      o.a_comp[0] = o.a_comp[1] = 0;
+      o.meta = 0;
+      o.sf_sparse = 0;
+      o.sf_res = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o.q_res[i] = o.q_sparse[i] = 0;
+      if (live) {
+        if (cached) {
+          const uint4 *row_cache = cache + (size_t)rl * row_vecs;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint4 v = row_cache[cache_slot(group, j)];
+            xw[4 * j + 0] = v.x;
+            xw[4 * j + 1] = v.y;
+            xw[4 * j + 2] = v.z;
+            xw[4 * j + 3] = v.w;
+          }
+        } else {
+          // plain loads: with kAdd these bytes were written by this CTA in phase 1
+          const uint4 *xs = reinterpret_cast<const uint4 *>(src + (size_t)row * k + (size_t)group * 32);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint4 v = xs[j];
+            xw[4 * j + 0] = v.x;
+            xw[4 * j + 1] = v.y;
+            xw[4 * j + 2] = v.z;
+            xw[4 * j + 3] = v.w;
+          }
+          if (kMode == 1) {
+            const float inv = inv_s[chunk_first_row(c) + rl];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint4 gv = gamma_s[cache_slot(group, j)];
+              const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint32_t w = xw[4 * j + q];
+                xw[4 * j + q] = pack_bf16x2(__fmul_rn(__fmul_rn(lo_f(w), inv), lo_f(gw[q])),
+                                            __fmul_rn(__fmul_rn(hi_f(w), inv), hi_f(gw[q])));
+              }
+            }
+          }
+        }
+        scale_group32(xw, scale, recip);
+        quantize_group32<false>(xw, tbl, o);
+      }
+      store_group(p, o, row, group, live, group < groups_padded, aligned_m, lane);
+    }
+  }
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------------------
@@ -546,13 +892,24 @@ __global__ void __launch_bounds__(kPrepareThreads, kPrepareCtasPerSm) prepare_ke
 
 size_t prepare_workspace_bytes(int m) { return 256 + (size_t)m * sizeof(float); }
 
-static int prepare_grid(const PrepareParams &p) {
+// SM count of the current device (queried once per device).
+static cudaError_t current_sms(int *dev_out, int *sms_out) {
   static int sms[64] = {};
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148 * kPrepareCtasPerSm;
-  if (sms[dev] == 0 && cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms[dev] = 148;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (sms[dev] == 0 && (e = cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+  *dev_out = dev;
+  *sms_out = sms[dev];
+  return cudaSuccess;
+}
+
+static int prepare_grid(const PrepareParams &p) {
+  int dev = 0, sms = 0;
   const int tiles = ((p.k + kColsPerCta - 1) / kColsPerCta) * p.row_tiles;
-  const int full = sms[dev] * kPrepareCtasPerSm;
+  if (current_sms(&dev, &sms) != cudaSuccess) return tiles < 1024 ? tiles : 1024;
+  const int full = sms * kPrepareCtasPerSm;
   return tiles < full ? tiles : full;
 }
 
@@ -595,6 +952,63 @@ cudaError_t run_prepare(const void *x, int m, int k, void *a_comp, void *e, void
   return launch_prepare(0, q_sparse_dense != nullptr, p, stream);
 }
 
+// One cooperative launch for statistics + prepare (see prepare_fused_kernel).  Returns
+// cudaErrorNotSupported when the shape does not fit or the device cannot launch it, in which
+// case the caller falls back to the separate statistics and prepare kernels.
+template <int kMode, bool kAdd>
+static cudaError_t launch_fused(const FusedParams &p_in, cudaStream_t stream) {
+  static bool attr_set[64] = {};
+  static int coop[64] = {};  // 0 unknown, 1 yes, -1 no
+  int dev = 0, sms = 0;
+  cudaError_t e = current_sms(&dev, &sms);
+  if (e != cudaSuccess) return e;
+  if (coop[dev] == 0) {
+    int v = 0;
+    coop[dev] = (cudaDeviceGetAttribute(&v, cudaDevAttrCooperativeLaunch, dev) == cudaSuccess && v) ? 1 : -1;
+  }
+  if (coop[dev] < 0) return cudaErrorNotSupported;
+  FusedParams p = p_in;
+  const int groups32 = p.k / 32;
+  p.rows_per_cta = (p.m + sms - 1) / sms;
+  const size_t row_bytes = (size_t)p.k * 2 + (kMode == 1 ? (size_t)(groups32 + 1) * 4 : 0);
+  const size_t fixed = (kMode == 1 ? (size_t)p.k * 2 + (size_t)p.rows_per_cta * 4 : 0);
+  if (fixed + row_bytes > (size_t)kFusedSmemBudget) return cudaErrorNotSupported;
+  const size_t capacity = ((size_t)kFusedSmemBudget - fixed) / row_bytes;
+  p.chunk_rows = (int)(capacity < (size_t)p.rows_per_cta ? capacity : (size_t)p.rows_per_cta);
+  const size_t smem = fixed + (size_t)p.chunk_rows * row_bytes + 16;
+  auto kernel = prepare_fused_kernel<kMode, kAdd>;
+  if (!attr_set[dev]) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFusedSmemBudget + 16);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.gridDim = dim3(sms);
+  cfg.blockDim = dim3(kFusedThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
+static bool fused_prepare_enabled() {
+  static const bool on = [] {
+    const char *v = getenv("SHARQ_PREPARE_FUSED");  // tuning hook: 0 selects the separate statistics + prepare kernels
+    return !(v != nullptr && v[0] == '0');
+  }();
+  return on;
+}
+
+int prepare_timeouts() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_prepare_timeouts, sizeof(v)) != cudaSuccess) return -1;
+  return v;
+}
+
 cudaError_t run_scaled_prepare(const void *x, const void *gamma, float eps, int m, int k, void *workspace,
                                float *inv_rms_external, void *a_comp, void *e, void *sfa_sparse, void *q_res,
                                void *sf_res, float *scale_out, cudaStream_t stream, bool absmax_ready,
@@ -608,6 +1022,32 @@ cudaError_t run_scaled_prepare(const void *x, const void *gamma, float eps, int 
   const bool rms = gamma != nullptr;
   // a small non-RMSNorm input (a decode step): the prepare kernel finds max|x| itself
   const bool inline_absmax = !rms && !absmax_ready && (size_t)m * k <= kInlineAbsmaxElements;
+  if (!absmax_ready && !inline_absmax && fused_prepare_enabled()) {
+    FusedParams f{};
+    f.x = static_cast<const __nv_bfloat16 *>(x);
+    f.residual = static_cast<const __nv_bfloat16 *>(residual);
+    f.sum_out = static_cast<__nv_bfloat16 *>(sum_out);
+    f.gamma = static_cast<const __nv_bfloat16 *>(gamma);
+    f.eps = eps;
+    f.inv_rms = inv_rms;
+    f.amax_bits = amax_bits;
+    f.arrive = amax_bits + 1;
+    f.scale_out = scale_out;
+    f.a_comp = static_cast<uint8_t *>(a_comp);
+    f.e = static_cast<uint8_t *>(e);
+    f.sfa_sparse = static_cast<uint8_t *>(sfa_sparse);
+    f.q_res = static_cast<uint8_t *>(q_res);
+    f.sf_res = static_cast<uint8_t *>(sf_res);
+    f.m = m;
+    f.k = k;
+    if ((err = cudaMemsetAsync(amax_bits, 0, 2 * sizeof(unsigned int), stream)) != cudaSuccess) return err;
+    err = !rms ? launch_fused<2, false>(f, stream)
+               : (residual != nullptr ? launch_fused<1, true>(f, stream) : launch_fused<1, false>(f, stream));
+    if (err == cudaSuccess) return cudaSuccess;
+    (void)cudaGetLastError();  // not launchable here: the separate kernels below do the same work
+    if (err != cudaErrorNotSupported && err != cudaErrorCooperativeLaunchTooLarge) return err;
+    err = cudaSuccess;
+  }
   if (absmax_ready) {
     // the producer of x already left max|x| in the workspace: no statistics pass
     if (rms) return cudaErrorInvalidValue;
@@ -631,7 +1071,9 @@ cudaError_t run_scaled_prepare(const void *x, const void *gamma, float eps, int 
   } else {
     const size_t n16 = (size_t)m * k / 8;
     size_t blocks = (n16 + 255) / 256;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    int dev = 0, sms = 0;
+    if (current_sms(&dev, &sms) != cudaSuccess) sms = 128;
+    if (blocks > (size_t)sms * 8) blocks = (size_t)sms * 8;
     abs_stats_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(x), n16, amax_bits);
   }
   err = cudaGetLastError();

@@ -6,7 +6,7 @@
 namespace sharq {
 
 // Bytes of scratch the scaled / RMSNorm-fused prepare needs for M rows:
-// [0,4) tensor absmax bits, [256, 256 + 4*M) per-row inv_rms.
+// [0,4) tensor absmax bits, [4,8) grid barrier counter, [256, 256 + 4*M) per-row inv_rms.
 size_t prepare_workspace_bytes(int m);
 
 // Prepare of an already scaled bf16 activation [m,k].  With q_sparse_dense != nullptr
@@ -23,5 +23,9 @@ cudaError_t run_scaled_prepare(const void *x, const void *gamma, float eps, int 
                                float *inv_rms_external, void *a_comp, void *e, void *sfa_sparse, void *q_res,
                                void *sf_res, float *scale_out, cudaStream_t stream, bool absmax_ready = false,
                                const void *residual = nullptr, void *sum_out = nullptr);
+
+// Grid barriers of the one-launch prepare that ran out on the current device since the library
+// was loaded (0 in a healthy process; -1 when the counter cannot be read).
+int prepare_timeouts();
 
 }  // namespace sharq
