@@ -55,12 +55,23 @@ int sharq_fused_sparse_residual_quantize_x(const void *x_bf16, int m, int n, int
 int sharq_fused_sparse_residual_quantize_x_debug(const void *x_bf16, int m, int n, int k, void *q_sparse,
                                                  void *sfa_sparse, void *q_res, void *sf_res, void *stream);
 
-/* Scratch bytes needed by the two scaled prepare calls below for M rows.  Layout:
- * bytes [0,4) tensor absmax (float bits), bytes [256, 256+4*M) per-row inv_rms (float). */
+/* Scratch bytes needed by the scaled prepare calls below for M rows.  Layout:
+ * bytes [0,4) tensor absmax (float bits), bytes [4,8) arrival counter of the grid-wide barrier,
+ * bytes [256, 256+4*M) per-row inv_rms (float).  The calls initialise what they use. */
 size_t sharq_prepare_workspace_bytes(int m);
 
+/* The scaled prepare calls run statistics and quantisation in ONE cooperative launch whose CTAs
+ * meet at a grid-wide barrier with a bounded wait (about one second).  Returns how many such
+ * waits ran out on the current device since the library was loaded: 0 in a healthy process (the
+ * outputs of a call that timed out are undefined), -1 if the counter cannot be read.  Synchronises
+ * nothing itself: call it after synchronising the stream.  No counterpart in the reference. */
+int sharq_prepare_timeouts(void);
+
 /* fused_rmsnorm_sparse_residual_quantize_x(X, rmsnorm_weight, eps, N): RMSNorm, tensor
- * scale = clamp(amax/2688, 1e-9) and prepare in two launches (row statistics, prepare).
+ * scale = clamp(amax/2688, 1e-9) and prepare: an 8-byte memset and one cooperative launch (row
+ * statistics, grid barrier, quantisation; the rows of a CTA stay in shared memory in between).
+ * The normalised values are divided by the float32 scale, as the reference's kernel does
+ * (kernels/src/fused_rmsnorm_sparse_prepare.cu:195-204).
  * K % 128 == 0 and K/32 <= 1024.  scale_out: one device float.  bindings.cpp:291-355 */
 int sharq_fused_rmsnorm_sparse_residual_quantize_x(const void *x_bf16, const void *rmsnorm_weight_bf16,
                                                    float rmsnorm_eps, int m, int n, int k, void *workspace,
@@ -79,9 +90,12 @@ int sharq_fused_add_rmsnorm_sparse_residual_quantize_x(const void *x_bf16, const
                                                        float *scale_out, void *stream);
 
 /* The non-RMSNorm activation path with its host-side passes folded in: computes
- * scale = clamp(max|X|/2688, 1e-9), X' = bf16(X/scale) and the prepare of X'.  Equals
+ * scale = clamp(max|X|/2688, 1e-9), X' = (X / scale).to(bf16) and the prepare of X'.  Equals
  * global_nvfp4_scale + divide + fused_sparse_residual_quantize_x of the reference
- * (model/quantize.py:179-183). */
+ * (model/quantize.py:43-44,179-183) as torch evaluates them on a CUDA device: dividing a bf16
+ * tensor by a 0-dim float32 tensor there casts the divisor to bf16 first, so X' =
+ * bf16(float(X) / float(bf16(scale))), while scale_out receives the unrounded float32 scale
+ * (which the reference multiplies into the GEMM output). */
 int sharq_scaled_sparse_residual_quantize_x(const void *x_bf16, int m, int n, int k, void *workspace,
                                             size_t workspace_bytes, void *a_comp, void *e, void *sfa_sparse,
                                             void *q_res, void *sf_res, float *scale_out, void *stream);

@@ -390,10 +390,15 @@ void sharq_oracle_rmsnorm_prepare(const uint16_t *x_bf16, const uint16_t *gamma_
 }
 
 /* Host-side pre-scaling of the non-RMSNorm path, model/quantize.py:179-183:
- * x' = bf16(float(x) / scale) with scale a float32 scalar (torch true division
- * of a bf16 tensor by a 0-dim float32 tensor computes in float and rounds to bf16). */
-void sharq_oracle_scale_bf16(const uint16_t *x_bf16, float scale, size_t n, uint16_t *out_bf16) {
-  for (size_t i = 0; i < n; ++i) out_bf16[i] = sharq_f32_to_bf16(sharq_bf16_to_f32(x_bf16[i]) / scale);
+ * x' = (x / scale).to(bf16) with x a bf16 tensor and scale a 0-dim float32 tensor.
+ * cuda_mode == 0: torch on the CPU divides float(x) by the float32 scale.
+ * cuda_mode != 0: torch on a CUDA device first casts the scale to the common dtype of the
+ * operation, bf16, and divides float(x) by float(bf16(scale)) (pinned by
+ * tests/golden/cuda_scale_division.npz, produced on a B200 by
+ * tests/golden/make_cuda_scale_division.py). */
+void sharq_oracle_scale_bf16(const uint16_t *x_bf16, float scale, size_t n, uint16_t *out_bf16, int cuda_mode) {
+  float div = cuda_mode ? sharq_bf16_to_f32(sharq_f32_to_bf16(scale)) : scale;
+  for (size_t i = 0; i < n; ++i) out_bf16[i] = sharq_f32_to_bf16(sharq_bf16_to_f32(x_bf16[i]) / div);
 }
 
 float sharq_oracle_absmax_bf16(const uint16_t *x_bf16, size_t n) {

@@ -166,10 +166,13 @@ def absmax_bf16(x_bits) -> np.float32:
     return np.float32(lib().sharq_oracle_absmax_bf16(_p(x_bits), x_bits.size))
 
 
-def scale_bf16(x_bits, scale: float) -> np.ndarray:
+def scale_bf16(x_bits, scale: float, cuda_mode: bool = False) -> np.ndarray:
+    """bf16(x / scale) as torch evaluates it for a bf16 tensor and a 0-dim float32 scale: on the CPU by the
+    float32 scale, on a CUDA device (cuda_mode) by the scale rounded to bf16."""
     x_bits = _u16(x_bits)
     out = np.empty_like(x_bits)
-    lib().sharq_oracle_scale_bf16(_p(x_bits), ctypes.c_float(float(scale)), ctypes.c_size_t(x_bits.size), _p(out))
+    lib().sharq_oracle_scale_bf16(_p(x_bits), ctypes.c_float(float(scale)), ctypes.c_size_t(x_bits.size), _p(out),
+                                  int(cuda_mode))
     return out
 
 

@@ -23,6 +23,7 @@ SIGNATURES = {
     "sharq_fused_sparse_residual_quantize_x": (c_int, [_P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P]),
     "sharq_fused_sparse_residual_quantize_x_debug": (c_int, [_P, c_int, c_int, c_int, _P, _P, _P, _P, _P]),
     "sharq_prepare_workspace_bytes": (c_size_t, [c_int]),
+    "sharq_prepare_timeouts": (c_int, []),
     "sharq_fused_rmsnorm_sparse_residual_quantize_x": (
         c_int, [_P, _P, c_float, c_int, c_int, c_int, _P, c_size_t, _P, _P, _P, _P, _P, _P, _P]),
     "sharq_scaled_sparse_residual_quantize_x": (

@@ -89,6 +89,8 @@ int sharq_fused_sparse_residual_quantize_x_debug(const void *x, int m, int n, in
 
 size_t sharq_prepare_workspace_bytes(int m) { return sharq::prepare_workspace_bytes(m); }
 
+int sharq_prepare_timeouts(void) { return sharq::prepare_timeouts(); }
+
 int sharq_fused_rmsnorm_sparse_residual_quantize_x(const void *x, const void *gamma, float eps, int m, int n, int k,
                                                    void *workspace, size_t workspace_bytes, void *a_comp, void *e,
                                                    void *sfa_sparse, void *q_res, void *sf_res, float *scale_out,

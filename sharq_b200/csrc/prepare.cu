@@ -206,6 +206,7 @@ struct GroupOut {
   uint32_t meta;         // 2 B metadata (4 nibbles)
   uint32_t sf_sparse;    // 1 B
   uint32_t sf_res;       // 2 B (first 16-group in the low byte)
+  uint32_t second_min;   // smallest (key - 4) of the second selected pair over the four chunks (see kTinyKey)
 };
 
 // four packed e2m1x2 bytes -> four half2 words (element 2i of byte i in the low half)
@@ -239,6 +240,7 @@ __device__ __forceinline__ void quantize_group32(const uint32_t (&xw)[16], const
   uint32_t lo_idx[4], hi_idx[4];
   uint32_t max_key = 0;
   uint32_t meta = 0;
+  uint32_t second_min = 0xFFFFFFFFu;
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     uint32_t key[4];
@@ -254,8 +256,10 @@ __device__ __forceinline__ void quantize_group32(const uint32_t (&xw)[16], const
     hi_idx[c] = max(ib, is);
     meta |= (lo_idx[c] | (hi_idx[c] << 2)) << (4 * c);
     max_key = max(max_key, best);
+    second_min = min(second_min, second - 4u);  // an all-zero pair (key < 4) wraps to a huge value
   }
   o.meta = meta;
+  o.second_min = second_min;
 
   // -- sparse main path scale (one UE4M3 per 32 logical elements)
   const uint32_t s_code = scale_code_from_max(__uint_as_float(max_key & 0xFFFF0000u));
@@ -312,22 +316,10 @@ __device__ __forceinline__ void quantize_group32(const uint32_t (&xw)[16], const
   o.sf_res = sf_res;
 }
 
-// bf16(y / scale) for the two halves of a packed word, y already bf16-exact floats.
+// bf16(y / scale) of a whole 32-element group, y already bf16-exact floats.
 // q = y * recip is within 2 ulp of the true quotient; when q is more than 4 ulp away from
 // every bf16 rounding boundary (low 16 bits == 0x8000) the IEEE quotient rounds to the same
-// bf16 value, otherwise the IEEE division is used.
-__device__ __forceinline__ uint32_t scaled_bf16x2(float ya, float yb, float scale, float recip) {
-  float qa = __fmul_rn(ya, recip), qb = __fmul_rn(yb, recip);
-  const uint32_t ta = (__float_as_uint(qa) + 0x8004u) & 0xFFFFu;
-  const uint32_t tb = (__float_as_uint(qb) + 0x8004u) & 0xFFFFu;
-  if (ta < 9u || tb < 9u) {
-    qa = __fdiv_rn(ya, scale);
-    qb = __fdiv_rn(yb, scale);
-  }
-  return pack_bf16x2(qa, qb);
-}
-
-// The same for a whole 32-element group with the boundary test done on packed halves: the low
+// bf16 value.  The boundary test is done on packed halves: the low
 // 16 bits of both products of a word go into one register (one byte permute), 0x8004 is added
 // to each half (a carry out of the low half can only raise the high half by one, which the
 // wider threshold absorbs), and a packed unsigned minimum over the group is compared once.
@@ -343,11 +335,77 @@ __device__ __forceinline__ void scale_group32(uint32_t (&w)[16], float scale, fl
     out[i] = pack_bf16x2(qa, qb);
   }
   if ((nearest & 0xFFFFu) < 10u || (nearest >> 16) < 10u) {
+    // Some product of this group is close to a rounding boundary (exact ties are common when
+    // the tensor absmax has a short mantissa).  Redo the words concerned with the correctly
+    // rounded quotient: two residual corrections q += (y - q*scale) * recip with fused
+    // multiply-adds (the classic division refinement, exact because recip is the correctly
+    // rounded reciprocal), or an IEEE division for tiny operands or a subnormal quotient.
 #pragma unroll
-    for (int i = 0; i < 16; ++i) out[i] = pack_bf16x2(__fdiv_rn(lo_f(w[i]), scale), __fdiv_rn(hi_f(w[i]), scale));
+    for (int i = 0; i < 16; ++i) {
+      const float ya = lo_f(w[i]), yb = hi_f(w[i]);
+      float qa = __fmul_rn(ya, recip), qb = __fmul_rn(yb, recip);
+      const uint32_t ta = (__float_as_uint(qa) + 0x8004u) & 0xFFFFu;
+      const uint32_t tb = (__float_as_uint(qb) + 0x8004u) & 0xFFFFu;
+      if (ta < 9u || tb < 9u) {
+        // residuals are exact for |y| >= 2^-100, and the refinement theorem needs a normal quotient
+        if (fminf(fabsf(ya), fabsf(yb)) < 7.8886090522101181e-31f || fminf(fabsf(qa), fabsf(qb)) < 2.3509887e-38f) {
+          qa = __fdiv_rn(ya, scale);
+          qb = __fdiv_rn(yb, scale);
+        } else {
+          qa = __fmaf_rn(__fmaf_rn(-qa, scale, ya), recip, qa);
+          qb = __fmaf_rn(__fmaf_rn(-qb, scale, yb), recip, qb);
+          qa = __fmaf_rn(__fmaf_rn(-qa, scale, ya), recip, qa);
+          qb = __fmaf_rn(__fmaf_rn(-qb, scale, yb), recip, qb);
+        }
+        out[i] = pack_bf16x2(qa, qb);
+      }
+    }
   }
 #pragma unroll
   for (int i = 0; i < 16; ++i) w[i] = out[i];
+}
+
+// A selected pair whose score is non-zero but below 2^-118 (key = float bits | pair index).
+constexpr uint32_t kTinyKey = 0x04800000u - 4u;
+
+// float(bf16(x)): the divisor of the non-RMSNorm path.  On a CUDA device `x / scale` with a bf16
+// tensor x and a 0-dim float32 tensor scale (model/quantize.py:179-183 of the reference) casts
+// the scale to the common dtype bf16 before dividing in float.
+__device__ __forceinline__ float round_to_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// Tensor-scale division and quantisation of one group.
+//   kMode 1: the divisor is the float32 scale (the reference's RMSNorm kernel divides by it with
+//            __fdiv_rn): products with a boundary test, see scale_group32.
+//   kMode 2: the divisor has an 8-bit significand (see round_to_bf16), and so has y.  The exact
+//            quotient of two such numbers is either representable in 8 bits or at least a
+//            relative 2^-17 away from every value with a 9-bit significand, i.e. from every bf16
+//            rounding boundary, while y * (1/div) is within 2^-22 of it: the product rounds to
+//            the same bf16 as the IEEE quotient, no test needed.  The argument needs a normal
+//            quotient; subnormal quotients only matter when such a value takes part in a pair
+//            selection, which the keys show (second_min): that group is redone with divisions.
+template <int kMode, bool kDebug>
+__device__ __forceinline__ void scale_quantize_group(uint32_t (&y)[16], float div, float recip, const ScaleTables &tbl,
+                                                     GroupOut &o) {
+  if (kMode == 1) {
+    scale_group32(y, div, recip);
+    quantize_group32<kDebug>(y, tbl, o);
+  } else if (kMode == 2) {
+    uint32_t q[16];
+#pragma unroll 1
+    for (int attempt = 0; attempt < 2; ++attempt) {
+      if (attempt == 0) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) q[i] = pack_bf16x2(__fmul_rn(lo_f(y[i]), recip), __fmul_rn(hi_f(y[i]), recip));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) q[i] = pack_bf16x2(__fdiv_rn(lo_f(y[i]), div), __fdiv_rn(hi_f(y[i]), div));
+      }
+      quantize_group32<kDebug>(q, tbl, o);
+      if (o.second_min >= kTinyKey) break;
+    }
+  } else {
+    quantize_group32<kDebug>(y, tbl, o);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -450,8 +508,9 @@ __global__ void __launch_bounds__(kPrepareThreads, kPrepareCtasPerSm) prepare_ke
     // ATen divides a CUDA tensor by a host scalar by multiplying with the float
     // reciprocal; clamp(min=1e-9) follows (kernels/src/bindings.cpp:337 of the reference).
     scale = fmaxf(__fmul_rn(amax, 1.0f / 2688.0f), 1.0e-9f);
-    recip = __frcp_rn(scale);
     if (p.scale_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *p.scale_out = scale;
+    if (kMode == 2) scale = round_to_bf16(scale);  // the divisor of the non-RMSNorm path, see round_to_bf16
+    recip = __frcp_rn(scale);
   }
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -514,15 +573,11 @@ __global__ void __launch_bounds__(kPrepareThreads, kPrepareCtasPerSm) prepare_ke
             const uint32_t w = xw[4 * j + t];
             const float a = __fmul_rn(__fmul_rn(lo_f(w), inv), lo_f(gw[t]));
             const float b = __fmul_rn(__fmul_rn(hi_f(w), inv), hi_f(gw[t]));
-            const uint32_t y = pack_bf16x2(a, b);
-            xw[4 * j + t] = scaled_bf16x2(lo_f(y), hi_f(y), scale, recip);
+            xw[4 * j + t] = pack_bf16x2(a, b);
           }
         }
-      } else if (kMode == 2) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) xw[i] = scaled_bf16x2(lo_f(xw[i]), hi_f(xw[i]), scale, recip);
       }
-      quantize_group32<kDebug>(xw, tbl, o);
+      scale_quantize_group<kMode, kDebug>(xw, scale, recip, tbl, o);
 
       uint4 q = make_uint4(o.q_res[0], o.q_res[1], o.q_res[2], o.q_res[3]);
       *reinterpret_cast<uint4 *>(p.q_res + (size_t)row * (k / 2) + (size_t)group * 16) = q;
@@ -577,8 +632,6 @@ __global__ void __launch_bounds__(kPrepareThreads, kPrepareCtasPerSm) prepare_ke
 // do not fit) from a second read of the input.  At 2048 x 4096 every row stays on chip, so
 // the input is read from HBM exactly once and the statistics cost no launch of their own.
 // ---------------------------------------------------------------------------
-constexpr int kFusedThreads = 512;
-constexpr int kFusedWarps = kFusedThreads / 32;
 constexpr int kFusedSmemBudget = 200 * 1024;       // dynamic shared memory the row cache may use
 constexpr long long kGridBarrierLimitCycles = 2000000000LL;  // about one second
 
@@ -638,20 +691,20 @@ __device__ __forceinline__ void store_group(const FusedParams &p, const GroupOut
   }
 }
 
-template <int kMode, bool kAdd>
+template <int kMode, bool kAdd, int kFusedThreads>
 __global__ void __launch_bounds__(kFusedThreads, 1) prepare_fused_kernel(const FusedParams p) {
   static_assert(kMode == 1 || kMode == 2, "modes with a statistics pass");
+  constexpr int kFusedWarps = kFusedThreads / 32;
   const int m = p.m, k = p.k;
   const int groups32 = k >> 5;
   const int groups_padded = ((k + 255) / 256) * 8;  // groups of the metadata tiles (256 columns each)
   const int aligned_m = (m + 127) / 128 * 128;
   const int row_vecs = k >> 3;                     // uint4 per row
-  const int partial_stride = groups32 + 1;         // padded: the row sums of different rows hit different banks
+  const int partial_stride = groups32 + 4;         // padded: 16-byte reads of neighbouring rows hit different banks
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   __shared__ ScaleTables tbl;
-  __shared__ float warp_red[kFusedWarps];
-  __shared__ int barrier_ok;
+  __shared__ float warp_red[32];
   extern __shared__ uint4 fused_smem[];
   uint4 *gamma_s = fused_smem;                                      // mode 1: k bf16, pieces permuted like the cache
   uint4 *cache = fused_smem + (kMode == 1 ? row_vecs : 0);          // chunk_rows x k bf16
@@ -703,62 +756,94 @@ __global__ void __launch_bounds__(kFusedThreads, 1) prepare_fused_kernel(const F
   auto chunk_first_row = [&](int c) { return c == 0 ? 0 : first_chunk_rows + (c - 1) * p.chunk_rows; };
   auto chunk_size = [&](int c) { return c == 0 ? first_chunk_rows : p.chunk_rows; };
   const __nv_bfloat16 *src = kAdd ? p.sum_out : p.x;  // what a second read of the (summed) input reads
-  __syncthreads();
+  // no barrier here: the tables and gamma are first read after the barriers of phase 1 / the grid barrier
 
   // ------------------------------------------------------------------ phase 1: statistics
   __nv_bfloat162 m2 = __floats2bfloat162_rn(0.0f, 0.0f);
   for (int c = 0; c < chunks; ++c) {
     const int c_rows = chunk_size(c), c_row0 = row_begin + chunk_first_row(c);
     if (c > 0) __syncthreads();  // the previous chunk's cache and partial sums are no longer read
-    for (int t = threadIdx.x; t < c_rows * groups32; t += kFusedThreads) {
-      const int rl = t / groups32, g = t - rl * groups32;
-      const size_t off = (size_t)(c_row0 + rl) * k + (size_t)g * 32;
-      const uint4 *xs = reinterpret_cast<const uint4 *>(p.x + off);
-      uint32_t w[16];
+    // two tasks (32-element groups) per iteration, all loads issued before the first use
+    const int n_tasks = c_rows * groups32;
+    for (int t0 = threadIdx.x; t0 < n_tasks; t0 += 2 * kFusedThreads) {
+      uint32_t w[2][16];
+      int rl[2], g[2];
+      bool on[2];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint4 v = __ldg(xs + j);
-        w[4 * j + 0] = v.x;
-        w[4 * j + 1] = v.y;
-        w[4 * j + 2] = v.z;
-        w[4 * j + 3] = v.w;
+      for (int u = 0; u < 2; ++u) {
+        const int t = t0 + u * kFusedThreads;
+        on[u] = t < n_tasks;
+        rl[u] = on[u] ? t / groups32 : 0;
+        g[u] = on[u] ? t - rl[u] * groups32 : 0;
       }
-      if (kAdd) {
-        const uint4 *rs = reinterpret_cast<const uint4 *>(p.residual + off);
-        uint4 *dst = reinterpret_cast<uint4 *>(p.sum_out + off);
+      uint4 xv[2][4], rv[2][4];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (on[u]) {
+          const size_t off = (size_t)(c_row0 + rl[u]) * k + (size_t)g[u] * 32;
+          const uint4 *xs = reinterpret_cast<const uint4 *>(p.x + off);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) xv[u][j] = __ldg(xs + j);
+          if (kAdd) {
+            const uint4 *rs = reinterpret_cast<const uint4 *>(p.residual + off);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) rv[u][j] = __ldg(rs + j);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (!on[u]) continue;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const uint4 r = __ldg(rs + j);
-          const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            w[4 * j + q] = pack_bf16x2(__fadd_rn(lo_f(w[4 * j + q]), lo_f(rw[q])), __fadd_rn(hi_f(w[4 * j + q]), hi_f(rw[q])));
-          dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+          w[u][4 * j + 0] = xv[u][j].x;
+          w[u][4 * j + 1] = xv[u][j].y;
+          w[u][4 * j + 2] = xv[u][j].z;
+          w[u][4 * j + 3] = xv[u][j].w;
         }
-      }
-      uint4 *row_cache = cache + (size_t)rl * row_vecs;
+        if (kAdd) {
+          uint4 *dst = reinterpret_cast<uint4 *>(p.sum_out + (size_t)(c_row0 + rl[u]) * k + (size_t)g[u] * 32);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) row_cache[cache_slot(g, j)] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-      if (kMode == 1) {
-        float s = 0.0f;
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t rw[4] = {rv[u][j].x, rv[u][j].y, rv[u][j].z, rv[u][j].w};
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float a = lo_f(w[i]), b = hi_f(w[i]);
-          s = __fmaf_rn(a, a, s);  // a*a is exact in float, so this equals s + a*a
-          s = __fmaf_rn(b, b, s);
+            for (int q = 0; q < 4; ++q)
+              w[u][4 * j + q] = pack_bf16x2(__fadd_rn(lo_f(w[u][4 * j + q]), lo_f(rw[q])),
+                                            __fadd_rn(hi_f(w[u][4 * j + q]), hi_f(rw[q])));
+            dst[j] = make_uint4(w[u][4 * j], w[u][4 * j + 1], w[u][4 * j + 2], w[u][4 * j + 3]);
+          }
         }
-        partial[rl * partial_stride + g] = s;
-      } else {
+        uint4 *row_cache = cache + (size_t)rl[u] * row_vecs;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) m2 = __hmax2(m2, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[i])));
+        for (int j = 0; j < 4; ++j)
+          row_cache[cache_slot(g[u], j)] = make_uint4(w[u][4 * j], w[u][4 * j + 1], w[u][4 * j + 2], w[u][4 * j + 3]);
+        if (kMode == 1) {
+          float sq = 0.0f;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float a = lo_f(w[u][i]), b = hi_f(w[u][i]);
+            sq = __fmaf_rn(a, a, sq);  // a*a is exact in float, so this equals sq + a*a
+            sq = __fmaf_rn(b, b, sq);
+          }
+          partial[rl[u] * partial_stride + g[u]] = sq;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) m2 = __hmax2(m2, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[u][i])));
+        }
       }
     }
     if (kMode == 1) {
       __syncthreads();
       if (threadIdx.x < c_rows) {
-        const float *pr = partial + threadIdx.x * partial_stride;
+        const float4 *pr = reinterpret_cast<const float4 *>(partial + threadIdx.x * partial_stride);
         float total = 0.0f;
-        for (int i = 0; i < groups32; ++i) total = __fadd_rn(total, pr[i]);
+        for (int i = 0; i < groups32 / 4; ++i) {  // groups32 is a multiple of 4 (K % 128 == 0)
+          const float4 v = pr[i];
+          total = __fadd_rn(total, v.x);
+          total = __fadd_rn(total, v.y);
+          total = __fadd_rn(total, v.z);
+          total = __fadd_rn(total, v.w);
+        }
         const float inv = rsqrtf(__fadd_rn(__fdiv_rn(total, (float)k), p.eps));
         inv_s[chunk_first_row(c) + threadIdx.x] = inv;
         p.inv_rms[c_row0 + threadIdx.x] = inv;
@@ -801,16 +886,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1) prepare_fused_kernel(const F
       if (mx > 0.0f) atomicMax(p.amax_bits, __float_as_uint(mx));
       __threadfence();
       atomicAdd(p.arrive, 1u);
-      int ok = 1;
       const long long t0 = clock64();
       while (ld_acquire_gpu(p.arrive) < gridDim.x) {
         if (clock64() - t0 > kGridBarrierLimitCycles) {
-          ok = 0;
           atomicAdd(&g_prepare_timeouts, 1);
           break;
         }
       }
-      barrier_ok = ok;
     }
     __syncthreads();
   }
@@ -818,8 +900,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) prepare_fused_kernel(const F
   // ATen divides a CUDA tensor by a host scalar by multiplying with the float
   // reciprocal; clamp(min=1e-9) follows (kernels/src/bindings.cpp:337 of the reference).
   const float scale = fmaxf(__fmul_rn(amax, 1.0f / 2688.0f), 1.0e-9f);
-  const float recip = __frcp_rn(scale);
   if (p.scale_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *p.scale_out = scale;
+  const float div = kMode == 2 ? round_to_bf16(scale) : scale;  // see round_to_bf16
+  const float recip = __frcp_rn(div);
 
   // ------------------------------------------------------------------ phase 2: quantise
   const int tasks_per_row = (groups_padded + 31) >> 5;  // a warp takes 32 neighbouring groups of one row
@@ -876,8 +959,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) prepare_fused_kernel(const F
             }
           }
         }
-        scale_group32(xw, scale, recip);
-        quantize_group32<false>(xw, tbl, o);
+        scale_quantize_group<kMode, false>(xw, div, recip, tbl, o);
       }
       store_group(p, o, row, group, live, group < groups_padded, aligned_m, lane);
     }
@@ -955,8 +1037,8 @@ cudaError_t run_prepare(const void *x, int m, int k, void *a_comp, void *e, void
 // One cooperative launch for statistics + prepare (see prepare_fused_kernel).  Returns
 // cudaErrorNotSupported when the shape does not fit or the device cannot launch it, in which
 // case the caller falls back to the separate statistics and prepare kernels.
-template <int kMode, bool kAdd>
-static cudaError_t launch_fused(const FusedParams &p_in, cudaStream_t stream) {
+template <int kMode, bool kAdd, int kThreads>
+static cudaError_t launch_fused_t(const FusedParams &p_in, cudaStream_t stream) {
   static bool attr_set[64] = {};
   static int coop[64] = {};  // 0 unknown, 1 yes, -1 no
   int dev = 0, sms = 0;
@@ -970,13 +1052,13 @@ static cudaError_t launch_fused(const FusedParams &p_in, cudaStream_t stream) {
   FusedParams p = p_in;
   const int groups32 = p.k / 32;
   p.rows_per_cta = (p.m + sms - 1) / sms;
-  const size_t row_bytes = (size_t)p.k * 2 + (kMode == 1 ? (size_t)(groups32 + 1) * 4 : 0);
+  const size_t row_bytes = (size_t)p.k * 2 + (kMode == 1 ? (size_t)(groups32 + 4) * 4 : 0);
   const size_t fixed = (kMode == 1 ? (size_t)p.k * 2 + (size_t)p.rows_per_cta * 4 : 0);
   if (fixed + row_bytes > (size_t)kFusedSmemBudget) return cudaErrorNotSupported;
   const size_t capacity = ((size_t)kFusedSmemBudget - fixed) / row_bytes;
   p.chunk_rows = (int)(capacity < (size_t)p.rows_per_cta ? capacity : (size_t)p.rows_per_cta);
   const size_t smem = fixed + (size_t)p.chunk_rows * row_bytes + 16;
-  auto kernel = prepare_fused_kernel<kMode, kAdd>;
+  auto kernel = prepare_fused_kernel<kMode, kAdd, kThreads>;
   if (!attr_set[dev]) {
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFusedSmemBudget + 16);
     if (e != cudaSuccess) return e;
@@ -987,12 +1069,31 @@ static cudaError_t launch_fused(const FusedParams &p_in, cudaStream_t stream) {
   attr[0].id = cudaLaunchAttributeCooperative;
   attr[0].val.cooperative = 1;
   cfg.gridDim = dim3(sms);
-  cfg.blockDim = dim3(kFusedThreads);
+  cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
+static int fused_threads() {
+  static const int t = [] {
+    const char *v = getenv("SHARQ_PREPARE_THREADS");  // tuning hook: 448, 512, 768 or 896 threads per CTA
+    const int n = v != nullptr ? atoi(v) : 0;
+    return (n == 448 || n == 512 || n == 768 || n == 896) ? n : 512;
+  }();
+  return t;
+}
+
+template <int kMode, bool kAdd>
+static cudaError_t launch_fused(const FusedParams &p, cudaStream_t stream) {
+  switch (fused_threads()) {
+    case 448: return launch_fused_t<kMode, kAdd, 448>(p, stream);
+    case 768: return launch_fused_t<kMode, kAdd, 768>(p, stream);
+    case 896: return launch_fused_t<kMode, kAdd, 896>(p, stream);
+    default: return launch_fused_t<kMode, kAdd, 512>(p, stream);
+  }
 }
 
 static bool fused_prepare_enabled() {

@@ -26,6 +26,7 @@ import torch
 from . import _lib
 
 _ERROR_FLAGS: dict[int, torch.Tensor] = {}
+_PREPARE_TIMEOUTS_SEEN = 0
 
 
 def _check(cond: bool, msg: str) -> None:
@@ -51,7 +52,15 @@ def _error_flag(device: torch.device) -> torch.Tensor:
 
 
 def check_device_errors(device=None) -> None:
-    """Synchronising check of the GEMM kernels' bounded-wait error flag."""
+    """Synchronising check of the kernels' bounded waits: the GEMM / all-reduce error flag of each
+    device and the grid barrier of the one-launch prepare."""
+    global _PREPARE_TIMEOUTS_SEEN
+    if torch.cuda.is_available() and torch.cuda.is_initialized():
+        torch.cuda.synchronize()
+        n = int(_lib.lib().sharq_prepare_timeouts())
+        if n > _PREPARE_TIMEOUTS_SEEN:
+            seen, _PREPARE_TIMEOUTS_SEEN = _PREPARE_TIMEOUTS_SEEN, n
+            raise RuntimeError(f"sharq_b200 prepare kernel: {n - seen} grid barrier wait(s) timed out; outputs are undefined")
     for idx, flag in list(_ERROR_FLAGS.items()):
         if device is not None and torch.device(device).index not in (None, idx):
             continue

@@ -161,3 +161,19 @@ def test_rmsnorm_stats_order_and_scale(oracle):
     assert np.allclose(inv, 1.0 / np.sqrt(want / 256 + 1e-6), rtol=1e-6)
     assert oracle.tensor_scale(2688.0, True) == np.float32(2688.0) * (np.float32(1.0) / np.float32(2688.0))
     assert oracle.tensor_scale(0.0, True) == np.float32(1e-9)
+
+
+def test_cuda_mode_scaling_matches_torch_on_a_cuda_device(oracle):
+    """tests/golden/cuda_scale_division.npz holds what torch returned on a B200 for the reference's
+    `(x / scale).to(bf16)`; the oracle's cuda_mode must reproduce every value, and the fixture
+    must really differ from the float32-scale division (else it would pin nothing)."""
+    from pathlib import Path
+
+    fix = np.load(Path(__file__).resolve().parent / "golden" / "cuda_scale_division.npz")
+    differs = 0
+    for i in range(8):
+        x, scale, q = fix[f"x{i}"], float(fix[f"scale{i}"]), fix[f"q{i}"]
+        assert oracle.tensor_scale(oracle.absmax_bf16(x), cuda_mode=True) == np.float32(scale)
+        assert np.array_equal(oracle.scale_bf16(x, scale, cuda_mode=True), q), i
+        differs += int((oracle.scale_bf16(x, scale, cuda_mode=False) != q).sum())
+    assert differs > 1000

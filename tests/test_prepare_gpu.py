@@ -147,8 +147,33 @@ def test_scaled_prepare_matches_oracle(oracle, m, k):
     got = [b.get() for b in bufs]
     s = oracle.tensor_scale(oracle.absmax_bf16(H.bits(x)), cuda_mode=True)
     assert scale.get().view(np.float32)[0] == s
-    want = oracle.prepare(oracle.scale_bf16(H.bits(x), s))
+    want = oracle.prepare(oracle.scale_bf16(H.bits(x), s, cuda_mode=True))
     _compare(got, want, f"scaled {m}x{k}")
+
+
+@pytest.mark.parametrize("cap", [64.0, 38.0, 84.0, 1.0, 255.0, 0.0030975341796875, 3.3895313892515355e38, 1.0e-30,
+                                 7.52316384526264e-37, 1.7e9, 2.0 ** 100])
+def test_scaled_prepare_division_is_ieee_for_every_bf16_value(cap):
+    """The tensor-scale division bf16(x / scale) inside the scaled prepare equals the IEEE
+    division ATen performs, for every finite bf16 value up to a given absmax (absmax values
+    with short mantissas make exact rounding ties frequent; tiny and huge ones reach the
+    subnormal guards).  Checked through the outputs: the scaled prepare must produce the bytes
+    of the plain prepare applied to torch's own quotient."""
+    from sharq_b200 import ops
+
+    allv = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(torch.bfloat16)
+    keep = allv[torch.isfinite(allv.float()) & (allv.float().abs() <= cap)]
+    assert keep.numel() > 0 and float(keep.float().abs().max()) > 0
+    m, k = 1024, 512  # more than 256 K elements: the one-launch kernel, not the small-input path
+    reps = (m * k + keep.numel() - 1) // keep.numel()
+    g = torch.Generator().manual_seed(3)
+    x = keep.repeat(reps)[torch.randperm(reps * keep.numel(), generator=g)][: m * k].reshape(m, k).contiguous().cuda()
+    got = ops.scaled_sparse_residual_quantize_x(x, 128)
+    scale = torch.clamp(x.abs().max().float() / (448.0 * 6.0), min=1e-9)
+    assert torch.equal(got[5].reshape(()), scale.reshape(()))
+    want = ops.fused_sparse_residual_quantize_x((x / scale).to(torch.bfloat16), 128)
+    for name, a, b in zip(("a_comp", "e", "sfa_sparse", "q_res", "sf_res"), got[:5], want):
+        assert torch.equal(a, b), (name, cap)
 
 
 def test_prepare_rejects_bad_k():
