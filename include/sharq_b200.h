@@ -235,6 +235,38 @@ size_t sharq_allreduce_flag_bytes(void);
 int sharq_allreduce_bf16_peer(void *const *rank_data_ptrs, void *const *rank_flag_ptrs, int rank, int world,
                               size_t n_bytes, int max_ctas, int *error_flag, void *stream);
 
+/* No counterpart in the reference (it has no tensor parallelism).  The transition between a
+ * row-parallel SharQ linear and the next column-parallel one over the GPUs of one NVSwitch
+ * domain, in ONE kernel per GPU, with the residual stream sharded by rows (GPU r owns rows
+ * [r*M/world, (r+1)*M/world)):
+ *   S   = in-switch fp32 sum over all GPUs of this GPU's rows of the partial products, rounded
+ *         to bf16 (partial_multicast: multicast address of the [M,K] bf16 partial-sum buffer,
+ *         which every GPU's row-parallel GEMM has written before this call on its stream)
+ *   X'  = bf16(residual_in + S) for this GPU's rows, written to residual_out [M/world, K]
+ *         (partial_multicast == NULL: X' = residual_in; residual_in == NULL: X' = S)
+ *   then RMSNorm statistics of X', the tensor scale from the absmax over ALL GPUs' rows, the
+ *   4:8 sparse + residual prepare of this GPU's rows, and the packed rows stored into EVERY
+ *   GPU's copy of the prepared activation.
+ * On return of the kernel every GPU's (a_comp, e, sfa_sparse, q_res, sf_res, *scale_out) hold
+ * exactly what sharq_fused_rmsnorm_sparse_residual_quantize_x produces for the whole [M,K]
+ * matrix X' on one GPU.  The five output buffers are this GPU's copy inside ONE symmetric
+ * allocation whose multicast mapping is at local address + multicast_delta; rank_state_ptrs[r]
+ * is GPU r's state block (sharq_tp_transition_state_bytes() bytes, in symmetric memory,
+ * zero-filled once, then owned by these calls) as mapped on this GPU.  workspace:
+ * sharq_tp_transition_workspace_bytes(M/world) bytes of local scratch.
+ * Requirements: M % (128*world) == 0, K % 128 == 0, K/32 <= 1024, 16-byte aligned buffers, the
+ * same sequence of calls on every GPU.  Every cross-GPU wait is bounded (about one second); one
+ * that runs out stores a code 0x301..0x306 in *error_flag and the outputs are undefined.  Uses
+ * multimem.ld_reduce / multimem.st and peer stores only. */
+size_t sharq_tp_transition_state_bytes(void);
+size_t sharq_tp_transition_workspace_bytes(int rows);
+int sharq_tp_reduce_rmsnorm_prepare_allgather(const void *partial_multicast, const void *residual_in_bf16,
+                                              void *residual_out_bf16, const void *rmsnorm_weight_bf16, float rmsnorm_eps,
+                                              int m, int n, int k, void *workspace, size_t workspace_bytes, void *a_comp,
+                                              void *e, void *sfa_sparse, void *q_res, void *sf_res,
+                                              long long multicast_delta, float *scale_out, void *const *rank_state_ptrs,
+                                              int rank, int world, int *error_flag, void *stream);
+
 /* Test/tuning hook: force the GEMM kernel variant (0 = automatic; 128 or 256 = single-CTA kernel
  * with that tile width; 512 = CTA-pair kernel, 256 x 256 tile per pair).  Process-wide. */
 int sharq_set_gemm_tile_n(int tile_n);

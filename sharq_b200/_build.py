@@ -15,7 +15,8 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB_DIR = PKG / "lib"
 LIB_PATH = LIB_DIR / "libsharq_b200.so"
-SOURCES = ["prepare.cu", "prepare_static.cu", "quant.cu", "gemm.cu", "allreduce.cu", "decoder_ops.cu", "c_api.cu"]
+SOURCES = ["prepare.cu", "prepare_static.cu", "sp_transition.cu", "quant.cu", "gemm.cu", "allreduce.cu", "decoder_ops.cu",
+           "c_api.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

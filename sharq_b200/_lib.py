@@ -6,7 +6,7 @@ call raises.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_float, c_int, c_int64, c_size_t, c_void_p, c_char_p, POINTER
+from ctypes import c_float, c_int, c_int64, c_longlong, c_size_t, c_void_p, c_char_p, POINTER
 from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
@@ -53,6 +53,11 @@ SIGNATURES = {
     "sharq_allreduce_bf16_multimem": (c_int, [_P, POINTER(c_void_p), c_int, c_int, c_size_t, c_int, _P, _P]),
     "sharq_allreduce_flag_bytes": (c_size_t, []),
     "sharq_allreduce_bf16_peer": (c_int, [POINTER(c_void_p), POINTER(c_void_p), c_int, c_int, c_size_t, c_int, _P, _P]),
+    "sharq_tp_transition_state_bytes": (c_size_t, []),
+    "sharq_tp_transition_workspace_bytes": (c_size_t, [c_int]),
+    "sharq_tp_reduce_rmsnorm_prepare_allgather": (
+        c_int, [_P, _P, _P, _P, c_float, c_int, c_int, c_int, _P, c_size_t, _P, _P, _P, _P, _P, c_longlong, _P,
+                POINTER(c_void_p), c_int, c_int, _P, _P]),
     "sharq_fused_rmsnorm_sparse_residual_quantize_x_noalloc": (
         c_int, [_P, _P, c_float, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P]),
     "sharq_noalloc_max_rows": (c_int, []),

@@ -12,6 +12,7 @@
 #include "gemm.cuh"
 #include "prepare.cuh"
 #include "quant.cuh"
+#include "sp_transition.cuh"
 
 namespace {
 
@@ -252,6 +253,59 @@ int sharq_allreduce_bf16_peer(void *const *rank_data_ptrs, void *const *rank_fla
   return check_cuda(sharq::run_allreduce(nullptr, rank_data_ptrs, rank_flag_ptrs, rank, world, n_bytes, max_ctas, error_flag,
                                          as_stream(stream)),
                     "allreduce_peer launch");
+}
+
+size_t sharq_tp_transition_state_bytes(void) { return sharq::sp_transition_state_bytes(); }
+
+size_t sharq_tp_transition_workspace_bytes(int rows) { return rows > 0 ? sharq::sp_transition_workspace_bytes(rows) : 0; }
+
+int sharq_tp_reduce_rmsnorm_prepare_allgather(const void *partial_multicast, const void *residual_in, void *residual_out,
+                                              const void *rmsnorm_weight, float eps, int m, int n, int k, void *workspace,
+                                              size_t workspace_bytes, void *a_comp, void *e, void *sfa_sparse, void *q_res,
+                                              void *sf_res, long long multicast_delta, float *scale_out,
+                                              void *const *rank_state_ptrs, int rank, int world, int *error_flag,
+                                              void *stream) {
+  (void)n;
+  SHARQ_REQUIRE(world >= 1 && world <= sharq::kSpMaxRanks, "world must be in [1, %d]", sharq::kSpMaxRanks);
+  SHARQ_REQUIRE(rank >= 0 && rank < world, "rank must be in [0, world)");
+  SHARQ_REQUIRE(m > 0 && k > 0 && m % (128 * world) == 0,
+                "M must be a positive multiple of 128 * world (every GPU owns whole 128-row bands), got M = %d, world = %d", m,
+                world);
+  SHARQ_REQUIRE(k % 128 == 0 && k / 32 <= 1024, "K must be a multiple of 128 with K/32 <= 1024, got %d", k);
+  SHARQ_REQUIRE(partial_multicast || residual_in, "partial sums or a residual (or both) must be given");
+  SHARQ_REQUIRE(residual_out && rmsnorm_weight && a_comp && e && sfa_sparse && q_res && sf_res && scale_out && rank_state_ptrs &&
+                    error_flag,
+                "null buffer");
+  SHARQ_REQUIRE(workspace && workspace_bytes >= sharq::sp_transition_workspace_bytes(m / world),
+                "workspace too small: need %zu bytes", sharq::sp_transition_workspace_bytes(m / world));
+  const void *aligned[] = {partial_multicast, residual_in, residual_out, rmsnorm_weight, a_comp, e, sfa_sparse, q_res, sf_res};
+  for (const void *ptr : aligned)
+    SHARQ_REQUIRE((reinterpret_cast<uintptr_t>(ptr) & 15) == 0, "buffers must be 16-byte aligned");
+  SHARQ_REQUIRE((multicast_delta & 15) == 0, "multicast_delta must be a multiple of 16");
+  for (int i = 0; i < world; ++i)
+    SHARQ_REQUIRE(rank_state_ptrs[i] != nullptr && (reinterpret_cast<uintptr_t>(rank_state_ptrs[i]) & 15) == 0,
+                  "rank_state_ptrs[%d] must be a 16-byte aligned pointer", i);
+  sharq::SpTransitionArgs a;
+  a.partial_multicast = partial_multicast;
+  a.residual_in = residual_in;
+  a.residual_out = residual_out;
+  a.gamma = rmsnorm_weight;
+  a.eps = eps;
+  a.workspace = workspace;
+  a.scale_out = scale_out;
+  a.a_comp = a_comp;
+  a.e = e;
+  a.sfa_sparse = sfa_sparse;
+  a.q_res = q_res;
+  a.sf_res = sf_res;
+  a.multicast_delta = multicast_delta;
+  a.rank_state_ptrs = rank_state_ptrs;
+  a.rank = rank;
+  a.world = world;
+  a.m = m;
+  a.k = k;
+  a.error_flag = error_flag;
+  return check_cuda(sharq::run_sp_transition(a, as_stream(stream)), "tp_reduce_rmsnorm_prepare_allgather launch");
 }
 
 int sharq_set_gemm_tile_n(int tile_n) {

@@ -205,6 +205,139 @@ def reserve_sum_buffer(group, device: torch.device, nbytes: int) -> Optional[Sym
 def release_sum_buffers() -> None:
     """Drop the shared symmetric buffers (call before destroying the process group)."""
     _SUM_BUFFERS.clear()
+    _SP_CONTEXTS.clear()
+
+
+class SequenceParallelContext:
+    """Symmetric-memory buffers and state of the one-kernel layer transition
+    (csrc/sp_transition.cu) for activations of a fixed shape [m, hidden]:
+
+    * `partial` - the [m, hidden] bf16 buffer the row-parallel GEMM (o_proj, down_proj) writes its
+      partial products into (pass `partial` as `out=` of the GEMM);
+    * the prepared activation of all m rows (A_comp, E, both scale buffers, Q_res), which
+      `transition` fills on every rank;
+    * the state words of the cross-rank hand-shakes.
+
+    The residual stream is sharded by rows: rank r owns rows [r*m/world, (r+1)*m/world).
+    Construction is collective (every rank, same arguments, outside stream capture).  Needs
+    m % (128 * world) == 0 and NVLink multicast; `supported` says whether a shape qualifies."""
+
+    @staticmethod
+    def supported(m: int, hidden: int, world: int) -> bool:
+        return world > 1 and m % (128 * world) == 0 and hidden % 128 == 0 and hidden // 32 <= 1024
+
+    def __init__(self, m: int, hidden: int, group, device: torch.device):
+        import torch.distributed._symmetric_memory as symm
+
+        from . import _lib, ops
+
+        group = group if group is not None else dist.group.WORLD
+        lib = _lib.lib()
+        self.group, self.device = group, device
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if not self.supported(m, hidden, self.world):
+            raise ValueError(f"activation [{m}, {hidden}] cannot be sharded by rows over {self.world} ranks")
+        self.m, self.hidden, self.rows = m, hidden, m // self.world
+        sizes = ops.get_fused_sparse_residual_buffer_sizes(m, hidden, hidden)  # (A_comp, E, SFA_sparse, Q_res, SF_res)
+
+        def up(n):
+            return (int(n) + 255) // 256 * 256
+
+        self._off = {}
+        cursor = 0
+        for name, nbytes in (("partial", m * hidden * 2), ("a_comp", sizes[0]), ("e", sizes[1]), ("sfa", sizes[2]),
+                             ("q_res", sizes[3]), ("sf_res", sizes[4]), ("state", int(lib.sharq_tp_transition_state_bytes()))):
+            self._off[name] = (cursor, int(nbytes))
+            cursor += up(nbytes)
+        self.storage = symm.empty(cursor, dtype=torch.uint8, device=device)
+        handle = symm.rendezvous(self.storage, group.group_name)
+        if not int(handle.multicast_ptr):
+            raise RuntimeError("symmetric memory has no NVLink multicast mapping on this system")
+        offset = int(getattr(handle, "offset", 0))
+        bases = [int(p) + offset for p in handle.buffer_ptrs]
+        if bases[self.rank] != self.storage.data_ptr():
+            raise RuntimeError("symmetric-memory handle does not describe the tensor it was made from")
+        self.handle = handle
+        self.multicast_delta = int(handle.multicast_ptr) + offset - bases[self.rank]
+        self.storage.zero_()  # the state words start at zero
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+        state_at = self._off["state"][0]
+        self.state_ptrs = (ctypes.c_void_p * self.world)(*[b + state_at for b in bases])
+        self.partial = self._view("partial").view(torch.bfloat16).view(m, hidden)
+        self.partial_multicast = self.storage.data_ptr() + self._off["partial"][0] + self.multicast_delta
+        self.scale = torch.zeros((), dtype=torch.float32, device=device)
+        self.workspace = torch.empty(int(lib.sharq_tp_transition_workspace_bytes(self.rows)), dtype=torch.uint8, device=device)
+
+    def _view(self, name: str) -> torch.Tensor:
+        begin, nbytes = self._off[name]
+        return self.storage[begin:begin + nbytes]
+
+    def row_bounds(self) -> Tuple[int, int]:
+        return self.rank * self.rows, (self.rank + 1) * self.rows
+
+    def transition(self, residual_local: Optional[torch.Tensor], gamma: torch.Tensor, eps: float, use_partial: bool = True,
+                   out_features_hint: int = 0):
+        """-> (prepared, new_residual_local).  prepared is the reference's ("SHARQ", A_comp, E, SFA_sparse,
+        Q_res, SF_res, scale) tuple for ALL m rows (views of this rank's symmetric buffers, valid until
+        the next transition); new_residual_local = bf16(residual_local + sum over ranks of `partial`)
+        for this rank's rows.  The row-parallel GEMM that wrote `partial` must precede this call on
+        the current stream of every rank."""
+        from . import _lib, ops
+
+        if residual_local is None and not use_partial:
+            raise ValueError("nothing to normalise: no partial sums and no residual")
+        if residual_local is not None and (residual_local.dtype != torch.bfloat16 or not residual_local.is_contiguous()
+                                           or tuple(residual_local.shape) != (self.rows, self.hidden)):
+            raise ValueError(f"residual_local must be a contiguous bf16 [{self.rows}, {self.hidden}] tensor")
+        if gamma.dtype != torch.bfloat16 or not gamma.is_contiguous() or gamma.numel() != self.hidden:
+            raise ValueError("gamma must be a contiguous bf16 vector of `hidden` elements")
+        new_residual = torch.empty((self.rows, self.hidden), dtype=torch.bfloat16, device=self.device)
+        a_comp, e, sfa, q_res, sf_res = (self._view(n) for n in ("a_comp", "e", "sfa", "q_res", "sf_res"))
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().sharq_tp_reduce_rmsnorm_prepare_allgather(
+                ctypes.c_void_p(self.partial_multicast) if use_partial else None,
+                None if residual_local is None else ctypes.c_void_p(residual_local.data_ptr()),
+                ctypes.c_void_p(new_residual.data_ptr()), ctypes.c_void_p(gamma.data_ptr()), float(eps), self.m,
+                int(out_features_hint), self.hidden, ctypes.c_void_p(self.workspace.data_ptr()), self.workspace.numel(),
+                ctypes.c_void_p(a_comp.data_ptr()), ctypes.c_void_p(e.data_ptr()), ctypes.c_void_p(sfa.data_ptr()),
+                ctypes.c_void_p(q_res.data_ptr()), ctypes.c_void_p(sf_res.data_ptr()), self.multicast_delta,
+                ctypes.c_void_p(self.scale.data_ptr()), self.state_ptrs, self.rank, self.world,
+                ctypes.c_void_p(ops._error_flag(self.device).data_ptr()),
+                ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)))
+        prepared = ("SHARQ", a_comp, e, sfa, q_res.view(self.m, self.hidden // 2), sf_res, self.scale)
+        return prepared, new_residual
+
+
+_SP_CONTEXTS = {}
+
+
+def sequence_parallel_context(m: int, hidden: int, group, device: torch.device) -> Optional[SequenceParallelContext]:
+    """The group's shared SequenceParallelContext for activations [m, hidden], created on first use
+    (collective, outside stream capture); None when the shape or the system does not qualify
+    (the ranks agree on that)."""
+    group = group if group is not None else dist.group.WORLD
+    key = (group.group_name, device.index, m, hidden)
+    if key in _SP_CONTEXTS:
+        return _SP_CONTEXTS[key]
+    world = dist.get_world_size(group)
+    ctx = None
+    if SequenceParallelContext.supported(m, hidden, world) and _multimem_wanted(group):
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("the sequence-parallel context must be created before stream capture")
+        err = None
+        try:
+            ctx = SequenceParallelContext(m, hidden, group, device)
+        except RuntimeError as exc:
+            ctx, err = None, exc
+        ok = torch.tensor([0 if ctx is None else 1], dtype=torch.int32, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if int(ok.item()) == 0:
+            ctx = None
+            if os.environ.get("SHARQ_TP_ALLREDUCE", "auto").lower() == "multimem":
+                raise RuntimeError(f"the sequence-parallel context could not be set up: {err}")
+    _SP_CONTEXTS[key] = ctx
+    return ctx
 
 
 class _ShardedBase(nn.Module):
