@@ -176,38 +176,83 @@ def run_ours(args):
 
     ob, oe = shard_bounds(HIDDEN, world, rank, 128)
     db, de = shard_bounds(FFN, world, rank, 128)
-    host = {"h": act(m, HIDDEN).pin_memory(), "o_in": act(m, HIDDEN)[:, ob:oe].contiguous().pin_memory(),
+    # Sequence-parallel tensor parallelism (N > 1): the residual stream is sharded by rows, and one
+    # kernel per GPU does reduce-scatter + residual add + RMSNorm prepare + all-gather of the packed
+    # activation between a row-parallel and the next column-parallel linear.  --tp-mode allreduce
+    # keeps the residual stream replicated (all-reduce kernel, every GPU prepares all rows).
+    sp = None
+    if world > 1 and args.tp_mode == "sp":
+        from sharq_b200.tp import sequence_parallel_context
+
+        sp = sequence_parallel_context(m, HIDDEN, None, dev)
+    tp_mode = "tp1" if world == 1 else ("sequence-parallel transition kernel" if sp is not None else "all-reduce kernel")
+    rb, re_ = (sp.row_bounds() if sp is not None else (0, m))
+    h_full = act(m, HIDDEN)
+    host = {"h": h_full[rb:re_].contiguous().pin_memory(), "o_in": act(m, HIDDEN)[:, ob:oe].contiguous().pin_memory(),
             "d_in": act(m, FFN)[:, db:de].contiguous().pin_memory()}
     devx = {k2: v.to(dev) for k2, v in host.items()}
-    out_host = torch.empty((m, HIDDEN), dtype=torch.bfloat16).pin_memory()
+    out_host = torch.empty((re_ - rb, HIDDEN), dtype=torch.bfloat16).pin_memory()
     h2d_bytes = sum(v.numel() * 2 for v in host.values())
     d2h_bytes = out_host.numel() * 2
 
+    class Timers:
+        """CUDA events around the prepare / transition and GEMM calls of one eager step."""
+
+        def __init__(self):
+            self.rows = []
+
+        def span(self, name, kind, fn):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = fn()
+            e1.record()
+            self.rows.append((name, kind, e0, e1))
+            return out
+
+    def run(timers, name, kind, fn):
+        return fn() if timers is None else timers.span(name, kind, fn)
+
     def step(x, timers=None):
-        y = None
-        for lw in layers:
-            for name, inp, gamma in (("qkv", "h", "gamma1"), ("o_proj", "o_in", None), ("gate_up", "h", "gamma2"),
-                                     ("down", "d_in", None)):
-                lin = lw[name]
-                if timers is not None:
-                    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-                    ev[0].record()
-                if gamma is not None:
-                    prep = lin.prepare_input_rmsnorm(x[inp], lw[gamma], eps)
-                else:
-                    prep = lin.local.prepare_input(x[inp])
-                if timers is not None:
-                    ev[1].record()
-                if gamma is None and timers is None:
-                    y = lin.apply_prepared_reduced(prep)  # GEMM + sum over ranks
-                else:
-                    y = lin.local.apply_prepared(prep)
-                if timers is not None:
-                    ev[2].record()
-                    timers.append((name, ev))
-                    if gamma is None:
-                        y = lin.reduce(y)
-        return y
+        """The linear path of the decoder as one chain: the (sharded) residual stream goes through
+        RMSNorm prepare -> qkv, o_proj -> add -> RMSNorm prepare -> gate_up, down -> add -> ...;
+        the attention and SwiGLU outputs that feed o_proj and down are the fixed inputs o_in / d_in."""
+        resid = x["h"]
+        n_layers = len(layers)
+        if sp is not None:
+            prep, resid = run(timers, "qkv", "prepare", lambda: sp.transition(resid, layers[0]["gamma1"], eps, use_partial=False))
+        elif world == 1:
+            prep = run(timers, "qkv", "prepare", lambda: layers[0]["qkv"].prepare_input_rmsnorm(resid, layers[0]["gamma1"], eps))
+        for i, lw in enumerate(layers):
+            nxt = layers[(i + 1) % n_layers]
+            if world > 1 and sp is None:  # replicated residual stream, all-reduce after the row-parallel linears
+                prep = run(timers, "qkv", "prepare", lambda: lw["qkv"].prepare_input_rmsnorm(x["h"], lw["gamma1"], eps))
+                run(timers, "qkv", "gemm", lambda: lw["qkv"].apply_prepared(prep))
+                po = run(timers, "o_proj", "prepare", lambda: lw["o_proj"].local.prepare_input(x["o_in"]))
+                run(timers, "o_proj", "gemm", lambda: lw["o_proj"].apply_prepared_reduced(po))
+                prep = run(timers, "gate_up", "prepare", lambda: lw["gate_up"].prepare_input_rmsnorm(x["h"], lw["gamma2"], eps))
+                run(timers, "gate_up", "gemm", lambda: lw["gate_up"].apply_prepared(prep))
+                pd = run(timers, "down", "prepare", lambda: lw["down"].local.prepare_input(x["d_in"]))
+                resid = run(timers, "down", "gemm", lambda: lw["down"].apply_prepared_reduced(pd))
+                continue
+            run(timers, "qkv", "gemm", lambda: lw["qkv"].apply_prepared(prep))
+            po = run(timers, "o_proj", "prepare", lambda: lw["o_proj"].local.prepare_input(x["o_in"]))
+            if sp is not None:
+                run(timers, "o_proj", "gemm", lambda: lw["o_proj"].local.apply_prepared(po, out=sp.partial))
+                prep, resid = run(timers, "gate_up", "prepare", lambda: sp.transition(resid, lw["gamma2"], eps))
+            else:
+                o = run(timers, "o_proj", "gemm", lambda: lw["o_proj"].local.apply_prepared(po))
+                prep, resid = run(timers, "gate_up", "prepare",
+                                  lambda: lw["gate_up"].local.prepare_input_add_rmsnorm(resid, o, lw["gamma2"], eps))
+            run(timers, "gate_up", "gemm", lambda: lw["gate_up"].apply_prepared(prep))
+            pd = run(timers, "down", "prepare", lambda: lw["down"].local.prepare_input(x["d_in"]))
+            if sp is not None:
+                run(timers, "down", "gemm", lambda: lw["down"].local.apply_prepared(pd, out=sp.partial))
+                prep, resid = run(timers, "qkv", "prepare", lambda: sp.transition(resid, nxt["gamma1"], eps))
+            else:
+                d = run(timers, "down", "gemm", lambda: lw["down"].local.apply_prepared(pd))
+                prep, resid = run(timers, "qkv", "prepare",
+                                  lambda: nxt["qkv"].local.prepare_input_add_rmsnorm(resid, d, nxt["gamma1"], eps))
+        return resid
 
     def barrier():
         if world > 1:
@@ -239,26 +284,48 @@ def run_ours(args):
         step(devx)
     ops.check_device_errors()
 
-    # ---- correctness of the sum over ranks (outside every timed region): one row-parallel
-    # output against the fp32 sum of the gathered per-rank partial products
+    # ---- correctness of the cross-GPU step (outside every timed region)
     tp_check = None
     if world > 1:
         lin = layers[0]["down"]
         prep = lin.local.prepare_input(devx["d_in"])
         partial = lin.local.apply_prepared(prep).clone()
-        reduced = lin.apply_prepared_reduced(prep).clone()
         parts = [torch.empty_like(partial) for _ in range(world)]
         dist.all_gather(parts, partial)
         want = torch.stack(parts).float().sum(0)
-        rel = float((reduced.float() - want).norm() / want.norm())
+        if sp is not None:
+            # transition kernel: (1) the new residual rows equal residual + sum of the partial products,
+            # (2) every rank's prepared activation of ALL rows is byte-identical to what one GPU
+            # computes (RMSNorm prepare op) for the gathered rows
+            sp.partial.copy_(partial)
+            prepared, new_rows = sp.transition(devx["h"], layers[0]["gamma1"], eps)
+            rows = [torch.empty_like(new_rows) for _ in range(world)]
+            dist.all_gather(rows, new_rows)
+            full = torch.cat(rows).contiguous()
+            want_rows = (h_full.to(dev).float() + want.to(torch.bfloat16).float()).to(torch.bfloat16)
+            rel = float((full.float() - want_rows.float()).norm() / want_rows.float().norm())
+            single = ops.fused_rmsnorm_sparse_residual_quantize_x(full, layers[0]["gamma1"], eps, HIDDEN)
+            same = all(torch.equal(a_.reshape(-1), b_.reshape(-1)) for a_, b_ in zip(prepared[1:6], single[:5]))
+            same = same and torch.equal(prepared[6].reshape(()), single[5].reshape(()))
+            good = rel <= 5e-3 and same and bool(torch.isfinite(full).all())
+            what = "transition kernel on the down_proj partial products of layer 0"
+            del rows, full, want_rows, single
+        else:
+            reduced = lin.apply_prepared_reduced(prep).clone()
+            rel = float((reduced.float() - want).norm() / want.norm())
+            same = None
+            good = rel <= 5e-3 and bool(torch.isfinite(reduced).all())
+            what = "all-reduced down_proj output of layer 0"
+            del reduced
         ops.check_device_errors()
-        flag = torch.tensor([1.0 if (rel <= 5e-3 and bool(torch.isfinite(reduced).all())) else 0.0], device=dev)
+        flag = torch.tensor([1.0 if good else 0.0], device=dev)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if float(flag.item()) != 1.0:
-            raise SystemExit(f"tp_check failed on rank {rank}: all-reduced down_proj output differs from the fp32 sum "
-                             f"of the partial products (relative Frobenius error {rel:.3e})")
-        tp_check = {"status": "ok", "layer": "down_proj of layer 0", "rel_fro_vs_fp32_sum": round(rel, 6), "tolerance": 5e-3}
-        del parts, want, partial, reduced, prep
+            raise SystemExit(f"tp_check failed on rank {rank}: {what}: relative Frobenius error {rel:.3e} against the fp32 "
+                             f"sum of the partial products, prepared bytes identical to the single-GPU prepare: {same}")
+        tp_check = {"status": "ok", "what": what, "rel_fro_vs_fp32_sum": round(rel, 6), "tolerance": 5e-3,
+                    "prepared_bytes_identical_to_single_gpu": same}
+        del parts, want, partial, prep
 
     # The step is launch-bound on the host once the work is split over several GPUs, so it is
     # captured once into a CUDA graph (kernels, memsets and the NCCL all-reduces) and replayed;
@@ -298,7 +365,7 @@ def run_ours(args):
     main_stream = torch.cuda.current_stream()
     copy_stream = torch.cuda.Stream()
     stage_in = [{k2: torch.empty_like(v) for k2, v in devx.items()} for _ in range(2)]
-    stage_out = [torch.empty((m, HIDDEN), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    stage_out = [torch.empty((re_ - rb, HIDDEN), dtype=torch.bfloat16, device=dev) for _ in range(2)]
     in_ready, in_free, out_ready, out_free = ([torch.cuda.Event() for _ in range(2)] for _ in range(4))
 
     def e2e_run(steps):
@@ -354,17 +421,16 @@ def run_ours(args):
     # ---- roofline pass: one more eager step with events around every prepare and GEMM call.  A
     # short device-side spin first lets the host run ahead, so that the events bracket kernel
     # time and not launch latency; per linear the median over the layers is used.
-    timers = []
+    timers = Timers()
     torch.cuda._sleep(20_000_000)
     step(devx, timers)
     torch.cuda.synchronize()
     ops.check_device_errors()
     peaks = load_peaks()
     samples = {}
-    for name, ev in timers:
+    for name, kind, e0, e1 in timers.rows:
         d = samples.setdefault(name, ([], []))
-        d[0].append(ev[0].elapsed_time(ev[1]))
-        d[1].append(ev[1].elapsed_time(ev[2]))
+        d[0 if kind == "prepare" else 1].append(e0.elapsed_time(e1))
 
     def median(v):
         v = sorted(v)
@@ -396,7 +462,10 @@ def run_ours(args):
         "prepare_rmsnorm": {"bound": "hbm", "achieved": round(prep_bytes / (prep_ms * 1e-3) / 1e9, 1),
                             "peak": peaks["hbm_gbs"], "unit": "GB/s",
                             "frac": round(prep_bytes / (prep_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
-                            "avg_ms_two_launches": round(prep_ms, 4)},
+                            "avg_ms": round(prep_ms, 4),
+                            "what": ("RMSNorm prepare with the residual add, one launch" if world == 1 else
+                                     "transition kernel: reduce-scatter + add + RMSNorm prepare + all-gather" if sp is not None
+                                     else "RMSNorm prepare of the replicated activation")},
         "per_linear_ms": {k2: {"prepare": round(v[0] / v[2], 4), "gemm": round(v[1] / v[2], 4)} for k2, v in per.items()},
         "gemm_time_share": round(gemm_share, 3),
     }
@@ -465,7 +534,7 @@ def run_ours(args):
         "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4", "data": "synthetic",
         "config": {"workload": f"llama3-8b linear layers (qkv 6144x4096, o 4096x4096, gate_up 28672x4096, "
                                f"down 4096x14336), M={m} tokens, {layers_n} layers per step, SharQ W4A4, RMSNorm fused",
-                   "parallelism": f"tp{world}", "launch": "eager" if graph is None else "one CUDA graph per step",
+                   "parallelism": f"tp{world}", "tp_mode": tp_mode, "launch": "eager" if graph is None else "one CUDA graph per step",
                    "l2": "inputs larger than L2: every layer has its own weights "
                                                       f"({layers_n} x 109 MB packed), no flush needed",
                    "tokens_per_s_linear_path": round(m / (ms_step * 1e-3), 1)},
@@ -473,9 +542,9 @@ def run_ours(args):
         "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": h2d_bytes,
                 "d2h_bytes_per_step": d2h_bytes, "ms_per_step": round(ms_e2e, 4),
                 "pipeline": "copies on a second stream, double-buffered: H2D of step i+1 and D2H of step i overlap kernels"},
-        # per layer: 4 linears x (statistics, prepare, GEMM) kernels, plus this project's all-reduce
-        # kernel after the two row-parallel linears when the work is sharded
-        "gpu_launches": args.steps * layers_n * (12 + (2 if world > 1 else 0)),
+        # per layer: 4 GEMMs, 2 scaled prepares, 2 RMSNorm prepares / transition kernels (replicated
+        # residual stream: 4 prepares and 2 all-reduce kernels)
+        "gpu_launches": args.steps * layers_n * (8 if (world == 1 or sp is not None) else 10),
         "clocks": clocks,
     }
     if tp_check is not None:
@@ -737,6 +806,8 @@ def main():
     ap.add_argument("--prefill-seq", type=int, default=0, help="sequence length of the prefill (0 = --tokens)")
     ap.add_argument("--compare", action="store_true", help="also time the prefill with dense NVFP4 and bf16 linears (1 GPU)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph replay")
+    ap.add_argument("--tp-mode", default="sp", choices=["sp", "allreduce"],
+                    help="N > 1: sequence-parallel transition kernel (default) or all-reduce with a replicated residual stream")
     ap.add_argument("--shape-sweep", action="store_true",
                     help="config-1 sweep (M in 16/128/2048/8192 x the four projection shapes) instead of the headline step")
     ap.add_argument("--kernel-table", action="store_true",

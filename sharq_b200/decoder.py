@@ -224,6 +224,26 @@ class SharqDecoderLayer(torch.nn.Module):
         return (x2 + d).view(b, s, h)
 
     @torch.no_grad()
+    def forward_sequence_parallel(self, sp, prepared, x_local: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, b: int,
+                                  s: int, next_gamma: torch.Tensor):
+        """One layer with the residual stream sharded by rows over the ranks (tp.SequenceParallelContext).
+        prepared: the RMSNorm-prepared input of qkv for ALL b*s rows (from the previous transition);
+        x_local: this rank's rows of the residual stream.  The two transitions (after o_proj with this
+        layer's post-attention norm, after down_proj with the NEXT layer's input norm) each run as one
+        kernel: reduce-scatter of the partial products, residual add, RMSNorm prepare of the local
+        rows, all-gather of the packed activation.  -> (prepared input of the next layer's qkv, x_local)."""
+        cfg = self.cfg
+        qkv = self.qkv.apply_prepared(prepared)
+        q, k, v = _split_heads(qkv, b, s, self.local_heads, self.local_kv, cfg.head_dim, cos, sin, True)
+        attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+        attn2 = attn.transpose(1, 2).reshape(b * s, self.local_heads * cfg.head_dim)
+        self.o_proj.local.apply_prepared(self.o_proj.local.prepare_input(attn2), out=sp.partial)
+        prepared, x_local = sp.transition(x_local, self.post_norm, cfg.eps)
+        gu = self.gate_up.apply_prepared(prepared)
+        self.down.local.apply_prepared(self.down.local.prepare_input_swiglu(gu), out=sp.partial)
+        return sp.transition(x_local, next_gamma, cfg.eps)
+
+    @torch.no_grad()
     def _moe(self, hn: torch.Tensor) -> torch.Tensor:
         """Sparse mixture of experts on the normalised hidden state [M, h] (routing as in
         model/qMixtralLayer.py:205-234): softmax over the router logits in float, top-k,
@@ -376,6 +396,7 @@ class SharqDecoder(torch.nn.Module):
         test run several ranks as threads of one process)."""
         super().__init__()
         self.cfg = cfg
+        self.world, self.mode, self.fused_glue, self.reduce_hook = world, mode, fused_glue, reduce_hook
         gen = torch.Generator(device=device).manual_seed(seed)
         self.embed = (0.02 * torch.randn(cfg.vocab, cfg.hidden, generator=gen, device=device)).to(torch.bfloat16)
         self.layers = torch.nn.ModuleList([SharqDecoderLayer(cfg, gen, device, world, rank, keep_reference, mode, fused_glue,
@@ -383,21 +404,53 @@ class SharqDecoder(torch.nn.Module):
         self.final_norm = (1 + 0.1 * torch.randn(cfg.hidden, generator=gen, device=device)).to(torch.bfloat16)
         self.lm_head = (0.02 * torch.randn(cfg.vocab, cfg.hidden, generator=gen, device=device)).to(torch.bfloat16)
 
+    def _sequence_parallel_context(self, m: int):
+        """The transition-kernel context for m tokens, or None when this model / shape / system keeps
+        the replicated residual stream (single rank, rank threads of a test, mixture of experts,
+        comparison modes, biases on row-parallel layers, m not a multiple of 128 * world)."""
+        import os
+
+        first = self.layers[0]
+        if (self.world == 1 or self.reduce_hook is not None or self.cfg.experts > 0 or self.mode != "SHARQ"
+                or not self.fused_glue or os.environ.get("SHARQ_TP_SEQUENCE_PARALLEL", "1") == "0"
+                or first.o_proj.bias is not None or first.down.bias is not None):
+            return None
+        from . import tp
+
+        return tp.sequence_parallel_context(m, self.cfg.hidden, None, self.embed.device)
+
     @torch.no_grad()
     def prefill(self, token_ids: torch.Tensor, reference: bool = False) -> torch.Tensor:
         """token_ids [B, S] -> logits of the last position [B, vocab] (float32).
         reference=True runs the unquantised bf16 layers (needs keep_reference=True)."""
         b, s = token_ids.shape
-        x = self.embed[token_ids]
-        cos, sin = rope_tables(s, self.cfg.head_dim, self.cfg.rope_theta, x.device)
-        delta = None
-        for layer in self.layers:
-            if reference:
-                x = layer.forward_reference(x, cos, sin)
-            else:
-                x, delta = layer(x, cos, sin, delta=delta, return_delta=True)
-        if delta is not None:
-            x = x + delta
-        last = x[:, -1, :].float()
+        cos, sin = rope_tables(s, self.cfg.head_dim, self.cfg.rope_theta, self.embed.device)
+        sp = None if reference else self._sequence_parallel_context(b * s)
+        if sp is not None:
+            import torch.distributed as dist
+
+            r0, r1 = sp.row_bounds()
+            x_local = self.embed[token_ids.reshape(-1)[r0:r1]].contiguous()
+            prepared, x_local = sp.transition(x_local, self.layers[0].input_norm, self.cfg.eps, use_partial=False)
+            for i, layer in enumerate(self.layers):
+                nxt = self.layers[i + 1].input_norm if i + 1 < len(self.layers) else self.final_norm
+                prepared, x_local = layer.forward_sequence_parallel(sp, prepared, x_local, cos, sin, b, s, nxt)
+            # the last position of every sequence lives on one rank: sum the zero-padded rows over ranks
+            last_rows = torch.arange(1, b + 1, device=x_local.device) * s - 1
+            mine = (last_rows >= r0) & (last_rows < r1)
+            last = torch.zeros((b, self.cfg.hidden), dtype=torch.float32, device=x_local.device)
+            last[mine] = x_local[last_rows[mine] - r0].float()
+            dist.all_reduce(last, op=dist.ReduceOp.SUM)
+        else:
+            x = self.embed[token_ids]
+            delta = None
+            for layer in self.layers:
+                if reference:
+                    x = layer.forward_reference(x, cos, sin)
+                else:
+                    x, delta = layer(x, cos, sin, delta=delta, return_delta=True)
+            if delta is not None:
+                x = x + delta
+            last = x[:, -1, :].float()
         last = last * torch.rsqrt(last.pow(2).mean(-1, keepdim=True) + self.cfg.eps) * self.final_norm.float()
         return (last.to(torch.bfloat16) @ self.lm_head.T).float()

@@ -115,6 +115,25 @@ def main():
             if not torch.equal(a.reshape(-1), b.reshape(-1)):
                 ok = False
                 say(f"graph replay: output {i} differs from the eager call")
+        # whole decoder: the sequence-parallel flow against the replicated residual stream (all-reduce)
+        from sharq_b200.decoder import DecoderConfig, SharqDecoder
+
+        cfg = DecoderConfig(hidden=512, layers=3, heads=8, kv_heads=4, head_dim=64, ffn=1024, vocab=1000)
+        model = SharqDecoder(cfg, dev, world=world, rank=rank, seed=5)
+        ids = torch.randint(0, cfg.vocab, (2, 64 * world), generator=torch.Generator().manual_seed(1)).to(dev)
+        logits_sp = model.prefill(ids)
+        if model._sequence_parallel_context(ids.numel()) is None:
+            ok = False
+            say("the decoder did not take the sequence-parallel path")
+        os.environ["SHARQ_TP_SEQUENCE_PARALLEL"] = "0"
+        logits_ar = model.prefill(ids)
+        os.environ["SHARQ_TP_SEQUENCE_PARALLEL"] = "1"
+        torch.cuda.synchronize()
+        ops.check_device_errors()
+        rel = float((logits_sp - logits_ar).norm() / logits_ar.norm())
+        if not (rel <= 2e-2 and bool(torch.isfinite(logits_sp).all())):
+            ok = False
+            say(f"decoder logits: sequence-parallel vs all-reduce relative error {rel}")
     except Exception as exc:  # no rank may leave while its memory is bound to the multicast object
         ok = False
         say(f"exception: {exc!r}")
