@@ -181,6 +181,8 @@ def run_ours(args):
     # activation between a row-parallel and the next column-parallel linear.  --tp-mode allreduce
     # keeps the residual stream replicated (all-reduce kernel, every GPU prepares all rows).
     sp = None
+    if args.tp_mode == "allreduce":
+        os.environ["SHARQ_TP_SEQUENCE_PARALLEL"] = "0"  # the whole-model prefill keeps the replicated residual stream too
     if world > 1 and args.tp_mode == "sp":
         from sharq_b200.tp import sequence_parallel_context
 

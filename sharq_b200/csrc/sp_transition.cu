@@ -194,68 +194,67 @@ __global__ void __launch_bounds__(kThreads, 1) sp_transition_kernel(const SpPara
   for (int c = 0; c < chunks; ++c) {
     const int c_rows = chunk_size(c), c_row0 = row_begin + chunk_first_row(c);
     if (c > 0) __syncthreads();
-    const int n_tasks = c_rows * groups32;
-    for (int t0 = threadIdx.x; t0 < n_tasks; t0 += 2 * kThreads) {
-      uint4 sv[2][4], rv[2][4] = {};
-      int rl[2], g[2];
-      bool on[2];
+    // 1a: reduce + add, 16 bytes per lane with neighbouring lanes on neighbouring addresses (the
+    // switch serves multimem requests best when a warp's request is contiguous); the new
+    // residual rows go to global memory and, group-permuted, into the shared-memory cache
+    const int n_vecs = c_rows * row_vecs;
+    constexpr int kInFlight = 4;
+    for (int v0 = threadIdx.x; v0 < n_vecs; v0 += kInFlight * kThreads) {
+      uint4 sv[kInFlight], rv[kInFlight];
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int t = t0 + u * kThreads;
-        on[u] = t < n_tasks;
-        rl[u] = on[u] ? t / groups32 : 0;
-        g[u] = on[u] ? t - rl[u] * groups32 : 0;
-      }
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        if (!on[u]) continue;
-        const size_t off_l = (size_t)(c_row0 + rl[u]) * k + (size_t)g[u] * 32;           // local row block
-        const size_t off_g = (size_t)(p.row0 + c_row0 + rl[u]) * k + (size_t)g[u] * 32;  // whole activation
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (p.partial_mc != nullptr)
-            ld_reduce_bf16x8(p.partial_mc + off_g * 2 + j * 16, sv[u][j]);
-          else
-            sv[u][j] = make_uint4(0u, 0u, 0u, 0u);
+      for (int u = 0; u < kInFlight; ++u) {
+        const int v = v0 + u * kThreads;
+        sv[u] = make_uint4(0u, 0u, 0u, 0u);
+        rv[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (v < n_vecs) {
+          const int rl = v / row_vecs, i = v - rl * row_vecs;
+          const size_t off_l = ((size_t)(c_row0 + rl) * row_vecs + i) * 16;           // bytes, local row block
+          const size_t off_g = ((size_t)(p.row0 + c_row0 + rl) * row_vecs + i) * 16;  // bytes, whole activation
+          if (p.partial_mc != nullptr) ld_reduce_bf16x8(p.partial_mc + off_g, sv[u]);
           if (p.residual_in != nullptr)
-            rv[u][j] = __ldg(reinterpret_cast<const uint4 *>(p.residual_in + off_l) + j);
+            rv[u] = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const uint8_t *>(p.residual_in) + off_l));
         }
       }
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        if (!on[u]) continue;
-        uint32_t w[16];
+      for (int u = 0; u < kInFlight; ++u) {
+        const int v = v0 + u * kThreads;
+        if (v >= n_vecs) continue;
+        const int rl = v / row_vecs, i = v - rl * row_vecs;
+        const uint32_t s4[4] = {sv[u].x, sv[u].y, sv[u].z, sv[u].w};
+        const uint32_t r4[4] = {rv[u].x, rv[u].y, rv[u].z, rv[u].w};
+        uint32_t w[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint32_t s4[4] = {sv[u][j].x, sv[u][j].y, sv[u][j].z, sv[u][j].w};
-          const uint32_t r4[4] = {rv[u][j].x, rv[u][j].y, rv[u][j].z, rv[u][j].w};
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            if (p.partial_mc == nullptr)
-              w[4 * j + q] = r4[q];
-            else if (p.residual_in == nullptr)
-              w[4 * j + q] = s4[q];
-            else  // bf16(residual + sum), rounded like the ATen add of two bf16 tensors
-              w[4 * j + q] = pack_bf16x2(__fadd_rn(lo_f(r4[q]), lo_f(s4[q])), __fadd_rn(hi_f(r4[q]), hi_f(s4[q])));
-          }
+        for (int q = 0; q < 4; ++q) {
+          if (p.partial_mc == nullptr)
+            w[q] = r4[q];
+          else if (p.residual_in == nullptr)
+            w[q] = s4[q];
+          else  // bf16(residual + sum), rounded like the ATen add of two bf16 tensors
+            w[q] = pack_bf16x2(__fadd_rn(lo_f(r4[q]), lo_f(s4[q])), __fadd_rn(hi_f(r4[q]), hi_f(s4[q])));
         }
-        uint4 *dst = reinterpret_cast<uint4 *>(p.residual_out + (size_t)(c_row0 + rl[u]) * k + (size_t)g[u] * 32);
-        uint4 *row_cache = cache + (size_t)rl[u] * row_vecs;
-        float sq = 0.0f;
+        const uint4 out = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.residual_out) + ((size_t)(c_row0 + rl) * row_vecs + i) * 16) = out;
+        cache[(size_t)rl * row_vecs + cache_slot(i >> 2, i & 3)] = out;
+      }
+    }
+    __syncthreads();
+    // 1b: sum of squares of every 32-element group in the reference's order
+    for (int t = threadIdx.x; t < c_rows * groups32; t += kThreads) {
+      const int rl = t / groups32, g = t - rl * groups32;
+      const uint4 *row_cache = cache + (size_t)rl * row_vecs;
+      float sq = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint4 v = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-          dst[j] = v;
-          row_cache[cache_slot(g[u], j)] = v;
-        }
+      for (int j = 0; j < 4; ++j) {
+        const uint4 xv = row_cache[cache_slot(g, j)];
+        const uint32_t w[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float a = lo_f(w[i]), b = hi_f(w[i]);
+        for (int q = 0; q < 4; ++q) {
+          const float a = lo_f(w[q]), b2 = hi_f(w[q]);
           sq = __fmaf_rn(a, a, sq);
-          sq = __fmaf_rn(b, b, sq);
+          sq = __fmaf_rn(b2, b2, sq);
         }
-        partial[rl[u] * partial_stride + g[u]] = sq;
       }
+      partial[rl * partial_stride + g] = sq;
     }
     __syncthreads();
     if (threadIdx.x < c_rows) {

@@ -436,10 +436,11 @@ class SharqDecoder(torch.nn.Module):
                 nxt = self.layers[i + 1].input_norm if i + 1 < len(self.layers) else self.final_norm
                 prepared, x_local = layer.forward_sequence_parallel(sp, prepared, x_local, cos, sin, b, s, nxt)
             # the last position of every sequence lives on one rank: sum the zero-padded rows over ranks
-            last_rows = torch.arange(1, b + 1, device=x_local.device) * s - 1
-            mine = (last_rows >= r0) & (last_rows < r1)
             last = torch.zeros((b, self.cfg.hidden), dtype=torch.float32, device=x_local.device)
-            last[mine] = x_local[last_rows[mine] - r0].float()
+            for bi in range(b):  # python indices only: this runs under stream capture
+                row = bi * s + s - 1
+                if r0 <= row < r1:
+                    last[bi].copy_(x_local[row - r0])
             dist.all_reduce(last, op=dist.ReduceOp.SUM)
         else:
             x = self.embed[token_ids]
