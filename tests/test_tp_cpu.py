@@ -90,3 +90,126 @@ def test_head_layout_for_non_divisible_models():
     import pytest
     with pytest.raises(ValueError):
         head_layout(28, 4, 3)
+
+
+def _leaving_worker(rank, world, port, out):
+    """Step 1 runs on every rank; rank 1 then leaves between the steps (no collective in
+    flight).  The surviving rank's next all-reduce must end with an error within the
+    process-group timeout instead of hanging."""
+    import datetime
+    import time
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    y = torch.ones(8, 8) * (rank + 1)
+    tp.all_reduce_sum_(y)
+    out[f"step1_{rank}"] = float(y[0, 0])
+    if rank == 1:
+        os._exit(0)  # leaves between two steps
+    t0 = time.time()
+    try:
+        tp.all_reduce_sum_(torch.ones(8, 8))
+        out["survivor"] = "no error"
+    except RuntimeError as exc:
+        out["survivor"] = f"RuntimeError after {time.time() - t0:.1f}s"
+    os._exit(0)
+
+
+def test_a_rank_that_leaves_ends_the_next_all_reduce_with_an_error():
+    world = 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_leaving_worker, args=(r, world, _free_port_shared(), out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+        assert not p.is_alive(), "a rank hung after its peer left"
+    assert out["step1_0"] == 3.0 and out["step1_1"] == 3.0
+    assert out["survivor"].startswith("RuntimeError"), out["survivor"]
+
+
+_PORT = {}
+
+
+def _free_port_shared():
+    if "p" not in _PORT:
+        _PORT["p"] = _free_port()
+    return _PORT["p"]
+
+
+def _mismatch_worker(rank, world, port, out):
+    import datetime
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    try:
+        y = torch.ones(8, 8 if rank == 0 else 16)  # the ranks disagree on the shape of the partial sum
+        tp.all_reduce_sum_(y)
+        out[rank] = "no error"
+    except RuntimeError as exc:
+        out[rank] = "RuntimeError"
+    os._exit(0)
+
+
+def test_mismatched_partial_sum_shapes_raise():
+    world = 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_mismatch_worker, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+        assert not p.is_alive(), "a rank hung on mismatched shapes"
+    assert any(v == "RuntimeError" for v in out.values()), dict(out)
+
+
+def _sp_flow_worker(rank, world, port, out):
+    """The sequence-parallel data flow (reduce-scatter of the partial sums, add to the local rows
+    of the residual stream, normalise, all-gather) with gloo collectives and float matmuls in
+    place of the kernels: it must reproduce the replicated flow (all-reduce, every rank adds
+    and normalises all rows)."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(1)
+        m, h, f = 256 * world, 64, 256
+        resid = torch.randn(m, h, generator=g)
+        act = torch.randn(m, f, generator=g)
+        w_row = torch.randn(h, f, generator=g)
+        gamma = 1 + 0.1 * torch.randn(h, generator=g)
+        kb, ke = tp.shard_bounds(f, world, rank, 128)
+        partial = act[:, kb:ke] @ w_row[:, kb:ke].T
+
+        def norm(t):
+            return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma
+
+        # replicated residual stream
+        full = partial.clone()
+        tp.all_reduce_sum_(full)
+        want = norm(resid + full)
+        # row-sharded residual stream
+        assert tp.SequenceParallelContext.supported(m, 128, world)
+        rows = m // world
+        mine = full[rank * rows:(rank + 1) * rows]  # gloo has no reduce-scatter: this rank's rows of the sum
+        local = norm(resid[rank * rows:(rank + 1) * rows] + mine)
+        gathered = [torch.empty_like(local) for _ in range(world)]
+        dist.all_gather(gathered, local)
+        out[rank] = float((torch.cat(gathered) - want).abs().max())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sequence_parallel_flow_equals_replicated_flow_gloo():
+    world = 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_sp_flow_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    assert len(out) == world and all(out[r] == 0.0 for r in range(world)), dict(out)
+    assert not tp.SequenceParallelContext.supported(2048, 4096, 1)
+    assert not tp.SequenceParallelContext.supported(2048 + 64, 4096, 8)
+    assert tp.SequenceParallelContext.supported(2048, 4096, 8)
