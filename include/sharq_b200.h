@@ -267,6 +267,11 @@ int sharq_tp_reduce_rmsnorm_prepare_allgather(const void *partial_multicast, con
                                               long long multicast_delta, float *scale_out, void *const *rank_state_ptrs,
                                               int rank, int world, int *error_flag, void *stream);
 
+/* Test/tuning hook: how many SM clock cycles a cross-GPU wait of the all-reduce and transition
+ * kernels may take before the kernel gives up, stores its error code and returns (0 restores the
+ * defaults of one to two seconds).  Applies to launches made after the call. */
+int sharq_set_wait_limit_cycles(long long cycles);
+
 /* Test/tuning hook: force the GEMM kernel variant (0 = automatic; 128 or 256 = single-CTA kernel
  * with that tile width; 512 = CTA-pair kernel, 256 x 256 tile per pair).  Process-wide. */
 int sharq_set_gemm_tile_n(int tile_n);

@@ -50,6 +50,7 @@ SIGNATURES = {
     "sharq_linear_gemm_ws": (
         c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_float, _P, _P, _P, _P, c_size_t, _P, _P]),
     "sharq_set_gemm_tile_n": (c_int, [c_int]),
+    "sharq_set_wait_limit_cycles": (c_int, [c_longlong]),
     "sharq_allreduce_bf16_multimem": (c_int, [_P, POINTER(c_void_p), c_int, c_int, c_size_t, c_int, _P, _P]),
     "sharq_allreduce_flag_bytes": (c_size_t, []),
     "sharq_allreduce_bf16_peer": (c_int, [POINTER(c_void_p), POINTER(c_void_p), c_int, c_int, c_size_t, c_int, _P, _P]),

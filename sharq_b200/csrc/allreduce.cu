@@ -30,6 +30,7 @@ namespace {
 constexpr int kThreads = 512;
 constexpr int kUnroll = 4;
 constexpr long long kSpinLimitCycles = 4000000000LL;  // about two seconds
+long long g_spin_limit_cycles = kSpinLimitCycles;     // host-side setting, see set_allreduce_wait_limit
 
 struct AllReduceParams {
   uint8_t *data[kAllReduceMaxRanks];      // peer-copy variant: rank p's buffer as mapped here
@@ -37,6 +38,7 @@ struct AllReduceParams {
   uint32_t *flags[kAllReduceMaxRanks];    // flags[p]: rank p's flag words as mapped here
   int rank, world;
   size_t slice_bytes;                     // bytes / world, multiple of 16
+  long long spin_limit;                   // clock cycles a flag wait may take
   int *error_flag;
 };
 
@@ -74,7 +76,7 @@ __device__ __forceinline__ void cross_rank_barrier(const AllReduceParams &p, uin
     const uint32_t *recv = p.flags[p.rank] + (size_t)blockIdx.x * p.world + peer;
     const long long t0 = clock64();
     while ((int32_t)(load_acquire(recv) - epoch) < 0) {
-      if (clock64() - t0 > kSpinLimitCycles) {
+      if (clock64() - t0 > p.spin_limit) {
         atomicExch(p.error_flag, code);
         break;
       }
@@ -170,6 +172,8 @@ __global__ void __launch_bounds__(kThreads) allreduce_multimem_kernel(const AllR
 
 }  // namespace
 
+void set_allreduce_wait_limit(long long cycles) { g_spin_limit_cycles = cycles > 0 ? cycles : kSpinLimitCycles; }
+
 size_t allreduce_flag_bytes() {
   return ((size_t)kAllReduceMaxCtas * kAllReduceMaxRanks + kAllReduceMaxCtas) * sizeof(uint32_t);
 }
@@ -186,6 +190,7 @@ cudaError_t run_allreduce(void *multicast_data, void *const *rank_data_ptrs, voi
   p.rank = rank;
   p.world = world;
   p.slice_bytes = bytes / world;
+  p.spin_limit = g_spin_limit_cycles;
   p.error_flag = error_flag;
   // about 128 KB of the slice per CTA, between 16 and the limit: measured best for a 16.8 MB
   // buffer (16 CTAs at 8 ranks: 54.9 us against 59.3 with 96; 64 CTAs at 2 ranks: 58.6 us

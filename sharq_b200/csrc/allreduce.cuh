@@ -11,6 +11,10 @@ constexpr int kAllReduceMaxCtas = 256;
 constexpr int kAllReduceDefaultCtas = 64;
 constexpr int kAllReducePeerMaxRanks = 4;  // the peer-copy variant keeps one 16-byte vector per rank in registers
 
+// Clock cycles a cross-rank flag wait may take before the kernel gives up with an error code
+// (0 restores the default of about two seconds).  Host-side setting for later launches.
+void set_allreduce_wait_limit(long long cycles);
+
 // bytes of flag words every rank must provide (zero-initialised once) next to its buffer
 size_t allreduce_flag_bytes();
 

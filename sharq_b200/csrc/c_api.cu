@@ -308,6 +308,13 @@ int sharq_tp_reduce_rmsnorm_prepare_allgather(const void *partial_multicast, con
   return check_cuda(sharq::run_sp_transition(a, as_stream(stream)), "tp_reduce_rmsnorm_prepare_allgather launch");
 }
 
+int sharq_set_wait_limit_cycles(long long cycles) {
+  SHARQ_REQUIRE(cycles >= 0, "cycles must be >= 0 (0 restores the defaults)");
+  sharq::set_allreduce_wait_limit(cycles);
+  sharq::set_sp_transition_wait_limit(cycles);
+  return 0;
+}
+
 int sharq_set_gemm_tile_n(int tile_n) {
   SHARQ_REQUIRE(tile_n == 0 || tile_n == 128 || tile_n == 256 || tile_n == 512, "tile_n must be 0, 128, 256 or 512");
   g_tile_n = tile_n;

@@ -46,6 +46,7 @@ constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
 constexpr int kSmemBudget = 200 * 1024;
 constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
+long long g_wait_limit_cycles = kWaitLimitCycles;     // host-side setting, see set_sp_transition_wait_limit
 
 // state words (uint32 index)
 constexpr int kReady = 0;        // [16] counters
@@ -71,6 +72,7 @@ struct SpParams {
   int m, k;                           // whole activation
   int row0, rows;                     // this GPU's row block
   int rows_per_cta, chunk_rows;
+  long long wait_limit;               // clock cycles a wait may take
   int *error_flag;
 };
 
@@ -108,12 +110,12 @@ __device__ __forceinline__ void st_release_sys64(uint32_t *p, unsigned long long
 }
 
 // Wait until the counter reaches `target` (wrap-safe).  False when the limit ran out.
-__device__ __forceinline__ bool wait_counter(const uint32_t *p, uint32_t target, bool gpu_scope) {
+__device__ __forceinline__ bool wait_counter(const uint32_t *p, uint32_t target, bool gpu_scope, long long limit) {
   const long long t0 = clock64();
   for (;;) {
     const uint32_t v = gpu_scope ? ld_acquire_gpu(p) : ld_acquire_sys(p);
     if ((int32_t)(v - target) >= 0) return true;
-    if (clock64() - t0 > kWaitLimitCycles) return false;
+    if (clock64() - t0 > limit) return false;
   }
 }
 
@@ -124,7 +126,7 @@ __device__ __forceinline__ void grid_barrier(const SpParams &p, uint32_t epoch, 
     uint32_t *arrive = p.state[p.rank] + kGridArrive;
     __threadfence();
     atomicAdd(arrive, 1u);
-    if (wait && !wait_counter(arrive, (epoch * 3u + (uint32_t)which) * gridDim.x, true)) atomicExch(p.error_flag, code);
+    if (wait && !wait_counter(arrive, (epoch * 3u + (uint32_t)which) * gridDim.x, true, p.wait_limit)) atomicExch(p.error_flag, code);
   }
   __syncthreads();
 }
@@ -177,7 +179,7 @@ __global__ void __launch_bounds__(kThreads, 1) sp_transition_kernel(const SpPara
   }
   // ---- A: wait for every GPU's partial sums
   if ((int)threadIdx.x < p.world) {
-    if (!wait_counter(my_state + kReady + threadIdx.x, tag, false)) atomicExch(p.error_flag, 0x301);
+    if (!wait_counter(my_state + kReady + threadIdx.x, tag, false, p.wait_limit)) atomicExch(p.error_flag, 0x301);
   }
   __syncthreads();
 
@@ -319,7 +321,7 @@ __global__ void __launch_bounds__(kThreads, 1) sp_transition_kernel(const SpPara
     for (;;) {
       v = ld_acquire_sys64(my_state + kAmax + 2 * threadIdx.x);
       if ((uint32_t)(v >> 32) == tag) break;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > p.wait_limit) {
         atomicExch(p.error_flag, 0x303);
         break;
       }
@@ -441,13 +443,13 @@ __global__ void __launch_bounds__(kThreads, 1) sp_transition_kernel(const SpPara
     atomicAdd(my_state + kGridArrive, 1u);
   }
   if (blockIdx.x == 0) {
-    if (threadIdx.x == 0 && !wait_counter(my_state + kGridArrive, (epoch * 3u + 3u) * gridDim.x, true))
+    if (threadIdx.x == 0 && !wait_counter(my_state + kGridArrive, (epoch * 3u + 3u) * gridDim.x, true, p.wait_limit))
       atomicExch(p.error_flag, 0x305);
     __syncthreads();
     if ((int)threadIdx.x < p.world) {
       __threadfence_system();
       signal_add_release(p.state[threadIdx.x] + kDone + p.rank);
-      if (!wait_counter(my_state + kDone + threadIdx.x, tag, false)) atomicExch(p.error_flag, 0x306);
+      if (!wait_counter(my_state + kDone + threadIdx.x, tag, false, p.wait_limit)) atomicExch(p.error_flag, 0x306);
     }
     __syncthreads();
     if (threadIdx.x == 0) *reinterpret_cast<volatile uint32_t *>(my_state + kEpoch) = tag;
@@ -455,6 +457,8 @@ __global__ void __launch_bounds__(kThreads, 1) sp_transition_kernel(const SpPara
 }
 
 }  // namespace
+
+void set_sp_transition_wait_limit(long long cycles) { g_wait_limit_cycles = cycles > 0 ? cycles : kWaitLimitCycles; }
 
 size_t sp_transition_state_bytes() { return (size_t)kStateWords * sizeof(uint32_t); }
 
@@ -496,6 +500,7 @@ cudaError_t run_sp_transition(const SpTransitionArgs &a, cudaStream_t stream) {
   p.rows = a.m / a.world;
   p.row0 = a.rank * p.rows;
   p.error_flag = a.error_flag;
+  p.wait_limit = g_wait_limit_cycles;
   const int groups32 = a.k / 32;
   p.rows_per_cta = (p.rows + sms - 1) / sms;
   const size_t row_bytes = (size_t)a.k * 2 + (size_t)(groups32 + 4) * 4;
