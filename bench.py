@@ -589,27 +589,63 @@ def run_ours(args):
 # CPU baseline / reference arm: the SHARQ_SIM fake-quant path (oracle port) on the host cores
 # ------------------------------------------------------------------------------------------------
 
-def cpu_baseline(seconds: float = 12.0, m: int = 128):
-    """SHARQ_SIM linear (RMSNorm + activation split + two bf16 matmuls) on the host cores."""
+def _reference_sim_layer(n: int, k: int, weight, with_norm: bool):
+    """The reference's own QLinearLayer(quant_type="SHARQ_SIM") from the staged copy of its Python
+    sources (oracle/_ref/py, put there by oracle/build_ref.py --stage-python), or None when the
+    staging is absent."""
     import torch
 
-    from oracle import sharq_sim as S
+    stage = ROOT / "oracle" / "_ref" / "py" / "model"
+    if not (stage / "qLinearLayer.py").exists():
+        return None
+    if str(stage) not in sys.path:
+        sys.path.insert(0, str(stage))
+    try:
+        from qLinearLayer import QLinearLayer  # the reference's module, unmodified
+    except Exception:
+        return None
+    lin = torch.nn.Linear(k, n, bias=False, dtype=torch.bfloat16)
+    with torch.no_grad():
+        lin.weight.copy_(weight)
+    return QLinearLayer(lin, quant_type="SHARQ_SIM")  # quantises the weight offline, untimed
+
+
+def _config0(m: int, n: int, k: int):
+    import torch
+
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(m, k, generator=g)
+    x[:, torch.randperm(k, generator=g)[: k // 100]] *= 20.0
+    gamma = (1 + 0.1 * torch.randn(k, generator=g)).to(torch.bfloat16)
+    w = (0.02 * torch.randn(n, k, generator=g)).to(torch.bfloat16)
+    return x.to(torch.bfloat16), gamma, w
+
+
+def cpu_baseline(seconds: float = 12.0, m: int = 512):
+    """Config 0: one SharQ linear in SHARQ_SIM mode on the host cores (X [512, 4096], RMSNorm, W [4096, 4096]):
+    the reference's own QLinearLayer when its sources are staged (kind "reference"), else the port."""
+    import torch
 
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    g = torch.Generator().manual_seed(0)
     n, k = HIDDEN, HIDDEN
-    x = torch.randn(m, k, generator=g)
-    x[:, torch.randperm(k, generator=g)[: k // 100]] *= 20.0
-    x = x.to(torch.bfloat16)
-    gamma = (1 + 0.1 * torch.randn(k, generator=g)).to(torch.bfloat16)
-    w = (0.02 * torch.randn(n, k, generator=g)).to(torch.bfloat16)
-    w_q, s_w = S.quantize_weight(w)  # offline, untimed
+    x, gamma, w = _config0(m, n, k)
+    layer = _reference_sim_layer(n, k, w, True)
+    if layer is not None:
+        kind, what = "reference", "the reference's QLinearLayer(quant_type='SHARQ_SIM').prepare_input_rmsnorm + apply_prepared"
 
-    def one():
-        xn = S.rmsnorm(x, gamma, 1e-6)
-        main, res, s_x = S.quantize_activation(xn)
-        return S.linear(main, res, s_x, w_q, s_w)
+        def one():
+            return layer.apply_prepared(layer.prepare_input_rmsnorm(x, gamma, 1e-6))
+    else:
+        from oracle import sharq_sim as S
+
+        kind, what = "port", "SHARQ_SIM port (oracle/sharq_sim.py)"
+        w_q, s_w = S.quantize_weight(w)  # offline, untimed
+
+        def one():
+            xn = S.rmsnorm(x, gamma, 1e-6)
+            main, res, s_x = S.quantize_activation(xn)
+            return S.linear(main, res, s_x, w_q, s_w)
 
     one()
     t0 = time.perf_counter()
@@ -618,8 +654,8 @@ def cpu_baseline(seconds: float = 12.0, m: int = 128):
         one()
         it += 1
     dt = (time.perf_counter() - t0) / it
-    return {"value": round(2.0 * m * n * k / dt / 1e12, 5), "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": f"SHARQ_SIM layer (oracle/sharq_sim.py), M={m}, K=N=4096, {it} iterations, weights pre-quantised"}
+    return {"value": round(2.0 * m * n * k / dt / 1e12, 5), "unit": UNIT, "cores": cores, "kind": kind,
+            "sample": f"config 0: {what}, M={m}, K=N=4096, {it} iterations, weights pre-quantised"}
 
 
 def run_shape_sweep(args):
@@ -739,12 +775,12 @@ def run_shape_sweep(args):
 
 
 def run_reference(args):
+    """Reference arm: the reference's CPU implementation of the path (SHARQ_SIM) on the host cores, on a
+    bounded sample of the workload: the four linears of ONE decoder layer at --ref-tokens tokens per step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     import torch
-
-    from oracle import sharq_sim as S
 
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
@@ -758,35 +794,51 @@ def run_reference(args):
 
     xs = {"h": act(m, HIDDEN), "o_in": act(m, HIDDEN), "d_in": act(m, FFN)}
     gamma = (1 + 0.1 * torch.randn(HIDDEN, generator=g)).to(torch.bfloat16)
-    weights = {}
-    for name, (n, k) in SHAPES.items():
-        weights[name] = S.quantize_weight((0.02 * torch.randn(n, k, generator=g)).to(torch.bfloat16))
+    raw = {name: (0.02 * torch.randn(n, k, generator=g)).to(torch.bfloat16) for name, (n, k) in SHAPES.items()}
+    layers = {name: _reference_sim_layer(raw[name].shape[0], raw[name].shape[1], raw[name], False) for name in SHAPES}
+    plan = (("qkv", "h", True), ("o_proj", "o_in", False), ("gate_up", "h", True), ("down", "d_in", False))
+    if all(v is not None for v in layers.values()):
+        kind, what = "reference", "the reference's own QLinearLayer(quant_type='SHARQ_SIM') (staged copy of its sources)"
 
-    def step():
-        y = None
-        for name, inp, norm in (("qkv", "h", True), ("o_proj", "o_in", False), ("gate_up", "h", True), ("down", "d_in", False)):
-            x = S.rmsnorm(xs[inp], gamma, 1e-6) if norm else xs[inp]
-            main, res, s_x = S.quantize_activation(x)
-            y = S.linear(main, res, s_x, *weights[name])
-        return y
+        def step():
+            y = None
+            for name, inp, norm in plan:
+                lay = layers[name]
+                prep = lay.prepare_input_rmsnorm(xs[inp], gamma, 1e-6) if norm else lay.prepare_input(xs[inp])
+                y = lay.apply_prepared(prep)
+            return y
+    else:
+        from oracle import sharq_sim as S
 
-    for _ in range(max(1, min(args.warmup, 2))):
+        kind, what = "port", "the SHARQ_SIM port (oracle/sharq_sim.py)"
+        weights = {name: S.quantize_weight(raw[name]) for name in SHAPES}
+
+        def step():
+            y = None
+            for name, inp, norm in plan:
+                x = S.rmsnorm(xs[inp], gamma, 1e-6) if norm else xs[inp]
+                main, res, s_x = S.quantize_activation(x)
+                y = S.linear(main, res, s_x, *weights[name])
+            return y
+
+    warm = max(1, min(args.warmup, 3))
+    for _ in range(warm):
         step()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         step()
     dt = (time.perf_counter() - t0) / args.steps
     value = flops_per_layer(m) / dt / 1e12
-    sample = (f"one decoder layer's four linears through the SHARQ_SIM port (oracle/sharq_sim.py) at M={m} tokens "
-              f"per step on {cores} host threads; weights pre-quantised")
+    sample = (f"one decoder layer's four linears through {what} at M={m} tokens per step on {cores} host threads; "
+              f"weights pre-quantised")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": round(value, 5), "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": max(1, min(args.warmup, 2)), "ms_per_step": round(dt * 1e3, 3),
+        "steps": args.steps, "warmup": warm, "ms_per_step": round(dt * 1e3, 3),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 fake-quant (SHARQ_SIM)",
         "data": "synthetic",
         "config": {"workload": "llama3-8b linear layers (qkv, o, gate_up, down), SHARQ_SIM on host CPU, "
                                f"bounded sample M={m} tokens, 1 layer per step"},
-        "cpu_baseline": {"value": round(value, 5), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": round(value, 5), "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": round(value, 5), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
 

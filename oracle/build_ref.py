@@ -3,6 +3,7 @@ compiled in place from the reference checkout (no source is copied) with a short
 recipe, plus the extern "C" shims of oracle/ref_wrap.cu.  TEST INFRASTRUCTURE ONLY.
 
     python oracle/build_ref.py [/path/to/reference] [--gemm]
+    python oracle/build_ref.py [/path/to/reference] --stage-python   # see stage_python()
 
 The reference needs NVIDIA CUTLASS, an un-vendored and unpinned submodule of its repository;
 the CUTLASS 4.5.0 headers shipped inside the flashinfer wheel are used instead (the version
@@ -74,6 +75,33 @@ def build(ref: Path = None, with_gemm: bool = False) -> None:
     print(OUT / name)
 
 
+PYTHON_FILES = ["sharq_loader.py", "model/quantize.py", "model/qLinearLayer.py", "model/hif4.py",
+                "benchmarks/correctness/example_fused_pairtop2_matrix_suite.py"]
+
+
+def stage_python(ref: Path = None) -> Path:
+    """Copies the reference's UNMODIFIED Python host code for the hot path (loader, QLinearLayer,
+    quantize glue, its matrix-suite correctness script) into the git-ignored oracle/_ref/py/, keeping
+    the directory layout, so that GPU tests can run it on top of this project's drop-in `sharq_ops`
+    module on a machine that has no reference checkout.  Nothing of it enters the repository."""
+    import shutil
+
+    ref = reference_dir() if ref is None else Path(ref)
+    out = OUT / "py"
+    for rel in PYTHON_FILES:
+        src = ref / rel
+        if not src.exists():
+            raise SystemExit(f"{src} not found; oracle/_ref/py not staged")
+        dst = out / rel
+        dst.parent.mkdir(parents=True, exist_ok=True)
+        shutil.copyfile(src, dst)
+    print(out)
+    return out
+
+
 if __name__ == "__main__":
     _args = [a for a in sys.argv[1:] if not a.startswith("--")]
-    build(Path(_args[0]) if _args else None, "--gemm" in sys.argv)
+    if "--stage-python" in sys.argv:
+        stage_python(Path(_args[0]) if _args else None)
+    else:
+        build(Path(_args[0]) if _args else None, "--gemm" in sys.argv)
