@@ -282,6 +282,7 @@ def run_ours(args):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    barrier()  # the ranks finish building their layers at different times
     for _ in range(max(args.warmup, 3)):
         step(devx)
     ops.check_device_errors()

@@ -255,7 +255,7 @@ int sharq_allreduce_bf16_peer(void *const *rank_data_ptrs, void *const *rank_fla
  * zero-filled once, then owned by these calls) as mapped on this GPU.  workspace:
  * sharq_tp_transition_workspace_bytes(M/world) bytes of local scratch.
  * Requirements: M % (128*world) == 0, K % 128 == 0, K/32 <= 1024, 16-byte aligned buffers, the
- * same sequence of calls on every GPU.  Every cross-GPU wait is bounded (about one second); one
+ * same sequence of calls on every GPU.  Every cross-GPU wait is bounded (about ten seconds); one
  * that runs out stores a code 0x301..0x306 in *error_flag and the outputs are undefined.  Uses
  * multimem.ld_reduce / multimem.st and peer stores only. */
 size_t sharq_tp_transition_state_bytes(void);
@@ -269,7 +269,7 @@ int sharq_tp_reduce_rmsnorm_prepare_allgather(const void *partial_multicast, con
 
 /* Test/tuning hook: how many SM clock cycles a cross-GPU wait of the all-reduce and transition
  * kernels may take before the kernel gives up, stores its error code and returns (0 restores the
- * defaults of one to two seconds).  Applies to launches made after the call. */
+ * defaults of two to ten seconds).  Applies to launches made after the call. */
 int sharq_set_wait_limit_cycles(long long cycles);
 
 /* Test/tuning hook: force the GEMM kernel variant (0 = automatic; 128 or 256 = single-CTA kernel

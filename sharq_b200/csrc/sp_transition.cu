@@ -26,7 +26,7 @@
 //   C  "broadcast landed": after its packed rows are stored to all GPUs, a GPU signals all
 //      others; CTA 0 waits for all of them before the kernel ends, so the GEMM that follows on
 //      the stream reads complete buffers.
-// Every wait is bounded (about one second); a wait that runs out sets *error_flag and the
+// Every wait is bounded (about ten seconds); a wait that runs out sets *error_flag and the
 // kernel carries on to its end (the result is then wrong, and the host sees the code).
 // Plain peer / multicast loads and stores only: no TMA touches another GPU's memory.
 #include <cuda_bf16.h>
@@ -45,7 +45,7 @@ namespace {
 constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
 constexpr int kSmemBudget = 200 * 1024;
-constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
+constexpr long long kWaitLimitCycles = 20000000000LL;  // about ten seconds: covers the skew between ranks that launch eagerly
 long long g_wait_limit_cycles = kWaitLimitCycles;     // host-side setting, see set_sp_transition_wait_limit
 
 // state words (uint32 index)

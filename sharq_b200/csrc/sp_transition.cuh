@@ -30,7 +30,7 @@ size_t sp_transition_state_bytes();
 // bytes of per-call scratch (per-row inv_rms of this GPU's rows)
 size_t sp_transition_workspace_bytes(int rows);
 
-// Clock cycles a wait of the kernel may take (0 restores the default of about one second).
+// Clock cycles a wait of the kernel may take (0 restores the default of about ten seconds).
 void set_sp_transition_wait_limit(long long cycles);
 
 cudaError_t run_sp_transition(const SpTransitionArgs &args, cudaStream_t stream);
