@@ -514,19 +514,22 @@ def run_ours(args):
         if pg is not None:
             pg.reset()
         del model
-        if args.compare and world == 1 and args.prefill_model == "llama3_8b" and p_batch == 1 and p_seq == m:
-            # the same stack with this project's dense-NVFP4 path and with plain bf16 linears
+        if args.compare and pcfg.experts == 0:
+            # the same stack with this project's dense-NVFP4 path and with plain bf16 linears, on the same
+            # number of GPUs (tensor-parallel shards, partial sums through the same all-reduce kernel)
             for mode in ("NVFP4", "BF16"):
                 torch.cuda.empty_cache()
-                other = SharqDecoder(DecoderConfig.llama3_8b(layers=layers_n), dev, seed=7, mode=mode)
+                other = SharqDecoder(make_cfg(layers=pcfg.layers), dev, world=world, rank=rank, seed=7, mode=mode)
                 for _ in range(2):
                     other.prefill(ids)
+                barrier()
                 og = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(og):
                     other.prefill(ids)
                 og.replay()
+                barrier()
                 ms_o = timed(lambda: og.replay(), args.prefill_steps) / args.prefill_steps
-                prefill[f"{mode.lower()}_tokens_per_s"] = round(m / (ms_o * 1e-3), 1)
+                prefill[f"{mode.lower()}_tokens_per_s"] = round(p_batch * p_seq / (ms_o * 1e-3), 1)
                 og.reset()
                 del other
 
@@ -859,7 +862,8 @@ def main():
                     help="architecture of the whole-model prefill measurement (random weights)")
     ap.add_argument("--prefill-batch", type=int, default=1)
     ap.add_argument("--prefill-seq", type=int, default=0, help="sequence length of the prefill (0 = --tokens)")
-    ap.add_argument("--compare", action="store_true", help="also time the prefill with dense NVFP4 and bf16 linears (1 GPU)")
+    ap.add_argument("--no-compare", dest="compare", action="store_false",
+                    help="skip timing the whole-model prefill with dense NVFP4 and with bf16 linears on the same GPUs")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph replay")
     ap.add_argument("--tp-mode", default="sp", choices=["sp", "allreduce"],
                     help="N > 1: sequence-parallel transition kernel (default) or all-reduce with a replicated residual stream")

@@ -82,8 +82,8 @@ class SharqDecoderLayer(torch.nn.Module):
         self.reduce_hook = reduce_hook
         if mode not in ("SHARQ", "NVFP4", "BF16"):
             raise ValueError(f"unknown mode {mode}")
-        if mode != "SHARQ" and world != 1:
-            raise ValueError("the NVFP4 and BF16 comparison modes are single-GPU only")
+        if mode != "SHARQ" and reduce_hook is not None:
+            raise ValueError("the NVFP4 and BF16 comparison modes run tensor-parallel only over a process group")
         self.mode = mode
         keep_reference = keep_reference or mode != "SHARQ"
         self.cfg, self.world, self.rank = cfg, world, rank
@@ -150,8 +150,14 @@ class SharqDecoderLayer(torch.nn.Module):
             wd = rnd(h, cfg.ffn)
             self.down = RowParallelSharqLinear(wd, local_columns=pad_rows(wd.T).T[:, fb:fe], world_rank=(world, rank),
                                                reduce_hook=reduce_hook)
-            if keep_reference:
+            if keep_reference and (mode == "SHARQ" or world == 1):
                 self.ref = dict(qkv=torch.cat((wq, wk, wv)), qkv_bias=full_bias, o=wo, gate=wg, up=wu, down=wd)
+            elif keep_reference:
+                # comparison modes under tensor parallelism: this rank's shards of the bf16 weights, cut
+                # like the SharQ layers (heads / padded FFN width column-parallel, o and down row-parallel)
+                self.ref = dict(qkv=torch.cat((head_rows(wq, q_ids), head_rows(wk, kv_ids), head_rows(wv, kv_ids))),
+                                qkv_bias=bias, o=wo_local.contiguous(), gate=pad_rows(wg)[fb:fe].contiguous(),
+                                up=pad_rows(wu)[fb:fe].contiguous(), down=pad_rows(wd.T).T[:, fb:fe].contiguous())
             del wq, wk, wv, wo, wg, wu, wd
         if mode == "NVFP4":
             # dense NVFP4 baseline: unfused RMSNorm, dense activation quantisation, dense GEMM
@@ -186,7 +192,10 @@ class SharqDecoderLayer(torch.nn.Module):
         if self.mode != "SHARQ":
             if delta is not None:
                 x = x + delta
-            y = self.forward_reference(x, cos, sin) if self.mode == "BF16" else self._forward_nvfp4(x, cos, sin)
+            if self.world > 1:
+                y = self._forward_comparison_tp(x, cos, sin)
+            else:
+                y = self.forward_reference(x, cos, sin) if self.mode == "BF16" else self._forward_nvfp4(x, cos, sin)
             return (y, None) if return_delta else y
         cfg = self.cfg
         b, s, h = x.shape
@@ -285,6 +294,55 @@ class SharqDecoderLayer(torch.nn.Module):
             else:
                 tp.all_reduce_sum_(out)
         return out
+
+    @torch.no_grad()
+    def _forward_comparison_tp(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        """The dense-NVFP4 or bf16 layer on this rank's weight shards: column-parallel qkv and gate_up,
+        row-parallel o_proj and down_proj whose partial outputs are written into symmetric memory and
+        summed by the same all-reduce kernel the SharQ layers use (torch.distributed where that is
+        not available)."""
+        from . import tp
+
+        cfg = self.cfg
+        b, s, h = x.shape
+        m = b * s
+        x2 = x.reshape(m, h)
+
+        def row_parallel(apply, n_out):
+            buf = tp.sum_buffer(None, x2.device, m * n_out * 2)
+            if buf is None:
+                y = apply(None)
+                tp.all_reduce_sum_(y)
+                return y
+            slot, view = buf.take(m, n_out)
+            apply(view)
+            buf.sum_(slot, m * n_out * 2)
+            return view
+
+        if self.mode == "BF16":
+            r = self.ref
+            qkv = F.linear(_rmsnorm(x2, self.input_norm, cfg.eps), r["qkv"], r["qkv_bias"])
+        else:
+            nv = self.nv
+            qkv = nv["qkv"].apply_prepared(nv["qkv"].prepare_input_rmsnorm(x2, self.input_norm, cfg.eps))
+        q, k, v = _split_heads(qkv, b, s, self.local_heads, self.local_kv, cfg.head_dim, cos, sin, self.fused_glue)
+        attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+        attn2 = attn.transpose(1, 2).reshape(m, self.local_heads * cfg.head_dim)
+        if self.mode == "BF16":
+            o = row_parallel(lambda out: torch.mm(attn2, r["o"].T, out=out) if out is not None else attn2 @ r["o"].T, h)
+        else:
+            po = nv["o"].prepare_input(attn2)
+            o = row_parallel(lambda out: nv["o"].apply_prepared(po, out=out), h)
+        x2 = x2 + o
+        if self.mode == "BF16":
+            gu = F.linear(_rmsnorm(x2, self.post_norm, cfg.eps), r["gate_up"])
+            hmid = _swiglu(gu, self.fused_glue).contiguous()
+            d = row_parallel(lambda out: torch.mm(hmid, r["down"].T, out=out) if out is not None else hmid @ r["down"].T, h)
+        else:
+            gu = nv["gate_up"].apply_prepared(nv["gate_up"].prepare_input_rmsnorm(x2, self.post_norm, cfg.eps))
+            pd = nv["down"].prepare_input(_swiglu(gu, self.fused_glue).contiguous())
+            d = row_parallel(lambda out: nv["down"].apply_prepared(pd, out=out), h)
+        return (x2 + d).view(b, s, h)
 
     @torch.no_grad()
     def _forward_nvfp4(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:

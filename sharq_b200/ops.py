@@ -410,10 +410,15 @@ def _gemm_scratch(M: int, N: int, dev):
     return (torch.empty(nbytes, dtype=torch.uint8, device=dev), nbytes) if nbytes else (None, 0)
 
 
-def _dense_gemm(A, B, SFA, SFB, alpha, alpha_t, C_in, beta):
+def _dense_gemm(A, B, SFA, SFB, alpha, alpha_t, C_in, beta, out=None):
     M, N, K = int(A.shape[0]), int(B.shape[0]), int(A.shape[1]) * 2
     dev = A.device
-    D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    if out is None:
+        D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    else:
+        _check(out.is_cuda and out.device == dev and out.dtype == torch.bfloat16 and out.is_contiguous()
+               and tuple(out.shape) == (M, N), "out must be a contiguous CUDA bfloat16 tensor shaped [M, N]")
+        D = out
     ws, ws_bytes = _gemm_scratch(M, N, dev)
     with _on_device(dev):
         _lib.check(_lib.lib().sharq_matmul_ws(
@@ -438,8 +443,9 @@ def matmul(A, B, SFA, SFB, scale: float):
     return _dense_gemm(A, B, SFA, SFB, scale, None, None, 0.0)
 
 
-def matmul_tensor_scale(A, B, SFA, SFB, scale: torch.Tensor):
-    return _dense_gemm(A, B, SFA, SFB, 1.0, scale, None, 0.0)
+def matmul_tensor_scale(A, B, SFA, SFB, scale: torch.Tensor, out: Optional[torch.Tensor] = None):
+    """out (not in the reference's op): optional bf16 [M, N] tensor to write into."""
+    return _dense_gemm(A, B, SFA, SFB, 1.0, scale, None, 0.0, out=out)
 
 
 def matmul_accum(A, B, SFA, SFB, scale: float, C_in, beta: float = 1.0):

@@ -141,8 +141,8 @@ class QLinearLayer(nn.Module):
         """out: optional bf16 [M, N] tensor the fused SharQ GEMM writes into (used by the
         tensor-parallel layers to place partial sums in symmetric memory)."""
         tag = prepared[0]
-        if out is not None and not (tag == "SHARQ" and self.fused_gemm):
-            raise ValueError("out= is only supported by the fused SharQ GEMM")
+        if out is not None and not ((tag == "SHARQ" and self.fused_gemm) or (tag == "NVFP4" and self.bias is None)):
+            raise ValueError("out= is only supported by the fused SharQ GEMM and the bias-free dense NVFP4 GEMM")
         if tag == "SHARQ":
             _, a_comp, e, sfa, q_res, sf_res, scale_x = prepared
             if self.fused_gemm:
@@ -161,7 +161,7 @@ class QLinearLayer(nn.Module):
         elif tag == "NVFP4":
             _, qx, scale_x, scale = prepared
             y = ops.matmul_tensor_scale(qx, self.weight_q, scale_x, self.scale_w,
-                                        (scale * self.weight_scale).reshape(1).contiguous())
+                                        (scale * self.weight_scale).reshape(1).contiguous(), out=out)
         else:
             raise ValueError(f"Unsupported prepared input tag: {tag}")
         if self.bias is not None:
