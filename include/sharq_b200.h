@@ -235,6 +235,37 @@ size_t sharq_allreduce_flag_bytes(void);
 int sharq_allreduce_bf16_peer(void *const *rank_data_ptrs, void *const *rank_flag_ptrs, int rank, int world,
                               size_t n_bytes, int max_ctas, int *error_flag, void *stream);
 
+/* Mixture-of-experts FFN in grouped launches.  The reference runs its experts in a Python loop
+ * (model/qMixtralLayer.py:223-231): per expert a gather of its tokens, prepare, two GEMMs, SwiGLU, a
+ * routing-weight multiply and index_add_.  These entry points do each step once for ALL experts on a
+ * GROUPED activation: the token slots are sorted by expert, every expert's segment is padded to a
+ * multiple of 256 rows, M is the padded total, and unit_group[u] (device, M/256 ints) is the expert
+ * of rows [256u, 256u+256) or < 0 for a unit without rows.  Arithmetic per row is that of the
+ * per-expert calls: every expert's rows are divided by that expert's own tensor scale.
+ *   sharq_grouped_sparse_residual_quantize_x: per-expert max|X| (into amax_workspace, `groups`
+ *     uint32 words) + scaled prepare; scale_vec_out[g] = clamp(amax_g / 2688, 1e-9).
+ *   sharq_grouped_swiglu_sparse_residual_quantize_x: H = silu(gate) * up of gate_up [M, 2K] (written
+ *     to h_bf16 [M, K]), per-expert max|H| and the scaled prepare of H.
+ *   sharq_linear_gemm_grouped: D[r] = alpha * alpha_vec[g] * (A_sparse[r] + A_res[r]) . W_g^T for every
+ *     row r of a unit of expert g (one launch; qw / sfw_sparse / sfw_dense: host arrays of `groups`
+ *     device pointers; alpha_vec: device, e.g. activation scale x weight scale per expert).
+ *   sharq_moe_combine: out[t] = sum over the top_k slots of token t, in ascending expert order, of
+ *     y[dest[t,j]] * w[t,j] with bf16 rounding after every product and addition, which is what the
+ *     reference's sequence of index_add_ calls on a zero buffer computes. */
+int sharq_grouped_sparse_residual_quantize_x(const void *x_bf16, int m, int n, int k, const int *unit_group, int groups,
+                                            void *amax_workspace, void *a_comp, void *e, void *sfa_sparse, void *q_res,
+                                            void *sf_res, float *scale_vec_out, void *stream);
+int sharq_grouped_swiglu_sparse_residual_quantize_x(const void *gate_up_bf16, int m, int n, int k, void *h_bf16,
+                                                   const int *unit_group, int groups, void *amax_workspace, void *a_comp,
+                                                   void *e, void *sfa_sparse, void *q_res, void *sf_res,
+                                                   float *scale_vec_out, void *stream);
+int sharq_linear_gemm_grouped(const void *a_comp, const void *e, const void *sfa_sparse, const void *q_res, const void *sf_res,
+                              int groups, const void *const *qw, const void *const *sfw_sparse, const void *const *sfw_dense,
+                              const int *unit_group, const float *alpha_vec, float alpha, int m, int n, int k, void *d,
+                              int *error_flag, void *stream);
+int sharq_moe_combine(void *out_bf16, const void *y_bf16, const int *dest, const int64_t *selected, const void *w_bf16,
+                      int tokens, int top_k, int width, void *stream);
+
 /* No counterpart in the reference (it has no tensor parallelism).  The transition between a
  * row-parallel SharQ linear and the next column-parallel one over the GPUs of one NVSwitch
  * domain, in ONE kernel per GPU, with the residual stream sharded by rows (GPU r owns rows

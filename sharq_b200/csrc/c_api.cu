@@ -255,6 +255,87 @@ int sharq_allreduce_bf16_peer(void *const *rank_data_ptrs, void *const *rank_fla
                     "allreduce_peer launch");
 }
 
+int sharq_grouped_sparse_residual_quantize_x(const void *x_bf16, int m, int n, int k, const int *unit_group, int groups,
+                                            void *amax_workspace, void *a_comp, void *e, void *sfa_sparse, void *q_res,
+                                            void *sf_res, float *scale_vec_out, void *stream) {
+  (void)n;
+  SHARQ_REQUIRE(m > 0 && m % 256 == 0 && k > 0 && k % 128 == 0, "M must be a positive multiple of 256 and K of 128");
+  SHARQ_REQUIRE(groups >= 1 && groups <= sharq::kGemmMaxGroups, "groups must be in [1, %d]", sharq::kGemmMaxGroups);
+  SHARQ_REQUIRE(x_bf16 && unit_group && amax_workspace && a_comp && e && sfa_sparse && q_res && sf_res && scale_vec_out,
+                "null buffer");
+  auto *amax = static_cast<unsigned int *>(amax_workspace);
+  if (check_cuda(sharq::run_abs_stats_grouped(x_bf16, m, k, amax, unit_group, groups, as_stream(stream)), "grouped absmax"))
+    return 1;
+  return check_cuda(sharq::run_grouped_prepare(x_bf16, m, k, amax, unit_group, groups, a_comp, e, sfa_sparse, q_res, sf_res,
+                                               scale_vec_out, as_stream(stream)),
+                    "grouped_sparse_residual_quantize_x");
+}
+
+int sharq_grouped_swiglu_sparse_residual_quantize_x(const void *gate_up_bf16, int m, int n, int k, void *h_bf16,
+                                                   const int *unit_group, int groups, void *amax_workspace, void *a_comp,
+                                                   void *e, void *sfa_sparse, void *q_res, void *sf_res,
+                                                   float *scale_vec_out, void *stream) {
+  (void)n;
+  SHARQ_REQUIRE(m > 0 && m % 256 == 0 && k > 0 && k % 128 == 0, "M must be a positive multiple of 256 and K of 128");
+  SHARQ_REQUIRE(groups >= 1 && groups <= sharq::kGemmMaxGroups, "groups must be in [1, %d]", sharq::kGemmMaxGroups);
+  SHARQ_REQUIRE(gate_up_bf16 && h_bf16 && unit_group && amax_workspace && a_comp && e && sfa_sparse && q_res && sf_res &&
+                    scale_vec_out,
+                "null buffer");
+  auto *amax = static_cast<unsigned int *>(amax_workspace);
+  if (check_cuda(sharq::run_swiglu_absmax(gate_up_bf16, m, k, 2LL * k, h_bf16, amax, as_stream(stream), unit_group, groups),
+                 "grouped swiglu"))
+    return 1;
+  return check_cuda(sharq::run_grouped_prepare(h_bf16, m, k, amax, unit_group, groups, a_comp, e, sfa_sparse, q_res, sf_res,
+                                               scale_vec_out, as_stream(stream)),
+                    "grouped_swiglu_sparse_residual_quantize_x");
+}
+
+int sharq_linear_gemm_grouped(const void *a_comp, const void *e, const void *sfa_sparse, const void *q_res, const void *sf_res,
+                              int groups, const void *const *qw, const void *const *sfw_sparse, const void *const *sfw_dense,
+                              const int *unit_group, const float *alpha_vec, float alpha, int m, int n, int k, void *d,
+                              int *error_flag, void *stream) {
+  SHARQ_REQUIRE(m > 0 && m % 256 == 0 && n > 0 && k > 0 && k % 128 == 0,
+                "M must be a positive multiple of 256, K a multiple of 128");
+  SHARQ_REQUIRE(groups >= 1 && groups <= sharq::kGemmMaxGroups, "groups must be in [1, %d]", sharq::kGemmMaxGroups);
+  SHARQ_REQUIRE(a_comp && e && sfa_sparse && q_res && sf_res && qw && sfw_sparse && sfw_dense && unit_group && alpha_vec && d &&
+                    error_flag,
+                "null buffer");
+  sharq::GroupedGemmArgs g;
+  g.a_comp = a_comp;
+  g.e = e;
+  g.sfa_sparse = sfa_sparse;
+  g.a_dense = q_res;
+  g.sfa_dense = sf_res;
+  g.groups = groups;
+  for (int i = 0; i < groups; ++i) {
+    SHARQ_REQUIRE(qw[i] && sfw_sparse[i] && sfw_dense[i], "weight buffers of group %d missing", i);
+    g.b[i] = qw[i];
+    g.sfb_sparse[i] = sfw_sparse[i];
+    g.sfb_dense[i] = sfw_dense[i];
+  }
+  g.unit_group = unit_group;
+  g.alpha_vec = alpha_vec;
+  g.alpha = alpha;
+  g.d = d;
+  g.m = m;
+  g.n = n;
+  g.k = k;
+  g.error_flag = error_flag;
+  return check_cuda(sharq::run_gemm_grouped(g, as_stream(stream)), "linear_gemm_grouped");
+}
+
+int sharq_moe_combine(void *out_bf16, const void *y_bf16, const int *dest, const int64_t *selected, const void *w_bf16,
+                      int tokens, int top_k, int width, void *stream) {
+  SHARQ_REQUIRE(out_bf16 && y_bf16 && dest && selected && w_bf16, "null buffer");
+  SHARQ_REQUIRE(tokens >= 0 && top_k >= 1 && top_k <= 8 && width > 0 && width % 8 == 0,
+                "tokens >= 0, top_k in [1, 8], width a positive multiple of 8");
+  SHARQ_REQUIRE(((reinterpret_cast<uintptr_t>(out_bf16) | reinterpret_cast<uintptr_t>(y_bf16)) & 15) == 0,
+                "out and y must be 16-byte aligned");
+  return check_cuda(sharq::run_moe_combine(out_bf16, y_bf16, dest, reinterpret_cast<const long long *>(selected), w_bf16, tokens,
+                                           top_k, width, as_stream(stream)),
+                    "moe_combine");
+}
+
 size_t sharq_tp_transition_state_bytes(void) { return sharq::sp_transition_state_bytes(); }
 
 size_t sharq_tp_transition_workspace_bytes(int rows) { return rows > 0 ? sharq::sp_transition_workspace_bytes(rows) : 0; }

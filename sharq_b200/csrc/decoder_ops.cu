@@ -107,14 +107,45 @@ __device__ __forceinline__ float silu_bf16(float x) {
   return round_bf16(v);
 }
 
+// CTA-wide maximum of a packed |value| accumulator, raised into *amax_bits (may be null).  All 256 threads call it.
+__device__ __forceinline__ void cta_absmax_to(float *warp_max, __nv_bfloat162 mx2, unsigned int *amax_bits) {
+  float mx = fmaxf(__bfloat162float(mx2.x), __bfloat162float(mx2.y));
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // warp_max may still be read by the previous call
+  if (lane == 0) warp_max[warp] = mx;
+  __syncthreads();
+  if (warp == 0) {
+    mx = lane < 8 ? warp_max[lane] : 0.0f;
+#pragma unroll
+    for (int off = 4; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    // non-negative floats order like their bit patterns
+    if (lane == 0 && amax_bits != nullptr) atomicMax(amax_bits, __float_as_uint(mx));
+  }
+}
+
+// With unit_group != nullptr (grouped activation of a mixture-of-experts layer: rows sorted by
+// group, 256-row units, unit_group[u] < 0 = no rows) a CTA takes chunks of kGroupedChunkRows
+// consecutive rows, skips chunks of empty units and raises amax_bits[group of the chunk].
+constexpr int kGroupedChunkRows = 64;
+
 __global__ void __launch_bounds__(256) swiglu_absmax_kernel(const __nv_bfloat16 *__restrict__ gate_up, long long rows,
                                                             int ffn, long long row_stride, __nv_bfloat16 *__restrict__ h,
-                                                            unsigned int *__restrict__ amax_bits) {
+                                                            unsigned int *__restrict__ amax_bits,
+                                                            const int *__restrict__ unit_group) {
   __shared__ float warp_max[8];
   const int vecs = ffn >> 3;
   __nv_bfloat162 mx2 = __floats2bfloat162_rn(0.0f, 0.0f);  // running max of |h|, two lanes
-  // a CTA walks rows, its threads the 16-byte vectors of a row, two vectors in flight per thread
-  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+  const bool grouped = unit_group != nullptr;
+  const long long n_chunks = grouped ? (rows + kGroupedChunkRows - 1) / kGroupedChunkRows : rows;
+  // a CTA walks rows (chunks of rows when grouped), its threads the 16-byte vectors of a row, two vectors in flight per thread
+  for (long long chunk = blockIdx.x; chunk < n_chunks; chunk += gridDim.x) {
+   const long long row_lo = grouped ? chunk * kGroupedChunkRows : chunk;
+   const long long row_hi = grouped ? min(rows, row_lo + kGroupedChunkRows) : chunk + 1;
+   const int grp = grouped ? unit_group[row_lo / 256] : 0;
+   if (grp < 0) continue;
+   for (long long row = row_lo; row < row_hi; ++row) {
     const __nv_bfloat16 *grow = gate_up + row * row_stride;
     __nv_bfloat16 *hrow = h + row * (long long)ffn;
     for (int v0 = threadIdx.x; v0 < vecs; v0 += 2 * blockDim.x) {
@@ -142,19 +173,77 @@ __global__ void __launch_bounds__(256) swiglu_absmax_kernel(const __nv_bfloat16 
         *reinterpret_cast<uint4 *>(hrow + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
       }
     }
+   }
+   if (grouped) {  // one reduction per chunk, into the chunk's group
+     cta_absmax_to(warp_max, mx2, amax_bits == nullptr ? nullptr : amax_bits + grp);
+     mx2 = __floats2bfloat162_rn(0.0f, 0.0f);
+   }
   }
-  float mx = fmaxf(__bfloat162float(mx2.x), __bfloat162float(mx2.y));
+  if (!grouped) cta_absmax_to(warp_max, mx2, amax_bits);
+}
+
+// Tensor absmax per group of a grouped bf16 activation [rows, width] (see swiglu_absmax_kernel).
+__global__ void __launch_bounds__(256) abs_stats_grouped_kernel(const __nv_bfloat16 *__restrict__ x, long long rows, int width,
+                                                                unsigned int *__restrict__ amax_bits,
+                                                                const int *__restrict__ unit_group) {
+  __shared__ float warp_max[8];
+  const int vecs = width >> 3;
+  const long long n_chunks = (rows + kGroupedChunkRows - 1) / kGroupedChunkRows;
+  for (long long chunk = blockIdx.x; chunk < n_chunks; chunk += gridDim.x) {
+    const long long row_lo = chunk * kGroupedChunkRows, row_hi = min(rows, row_lo + kGroupedChunkRows);
+    const int grp = unit_group[row_lo / 256];
+    if (grp < 0) continue;
+    __nv_bfloat162 mx2 = __floats2bfloat162_rn(0.0f, 0.0f);
+    const uint4 *src = reinterpret_cast<const uint4 *>(x + row_lo * width);
+    const long long n16 = (row_hi - row_lo) * vecs;
+    for (long long i = threadIdx.x; i < n16; i += blockDim.x) {
+      const uint4 v = __ldg(src + i);
+      mx2 = __hmax2(mx2, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&v.x)));
+      mx2 = __hmax2(mx2, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&v.y)));
+      mx2 = __hmax2(mx2, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&v.z)));
+      mx2 = __hmax2(mx2, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&v.w)));
+    }
+    cta_absmax_to(warp_max, mx2, amax_bits + grp);
+  }
+}
+
+// Output of a grouped mixture-of-experts FFN back into token order: token t sums its top_k expert
+// outputs y[dest[t, j], :] * w[t, j] in ascending order of the expert index, every product and every
+// partial sum rounded to bf16 - the arithmetic of the reference's per-expert loop
+// `final.index_add_(0, top_x, y * w[top_x, idx, None])` (model/qMixtralLayer.py:223-231), which
+// visits the experts in that order on a zero-initialised buffer.
+constexpr int kCombineMaxTopK = 8;
+__global__ void __launch_bounds__(256) moe_combine_kernel(__nv_bfloat16 *__restrict__ out, const __nv_bfloat16 *__restrict__ y,
+                                                          const int *__restrict__ dest, const long long *__restrict__ selected,
+                                                          const __nv_bfloat16 *__restrict__ w, long long tokens, int top_k,
+                                                          int width) {
+  const int vecs = width >> 3;
+  for (long long t = blockIdx.x; t < tokens; t += gridDim.x) {
+    // slots of this token in ascending expert order (every thread computes the same tiny sort)
+    int order[kCombineMaxTopK];
+    for (int j = 0; j < top_k; ++j) order[j] = j;
+    for (int a = 1; a < top_k; ++a)
+      for (int b = a; b > 0 && selected[t * top_k + order[b]] < selected[t * top_k + order[b - 1]]; --b) {
+        const int tmp = order[b];
+        order[b] = order[b - 1];
+        order[b - 1] = tmp;
+      }
+    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int j = 0; j < top_k; ++j) {
+        const int slot = order[j];
+        const float wj = __bfloat162float(w[t * top_k + slot]);
+        const uint4 yv = __ldg(reinterpret_cast<const uint4 *>(y + (long long)dest[t * top_k + slot] * width) + v);
+        const uint32_t yw[4] = {yv.x, yv.y, yv.z, yv.w};
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (lane == 0) warp_max[warp] = mx;
-  __syncthreads();
-  if (warp == 0) {
-    mx = lane < 8 ? warp_max[lane] : 0.0f;
-#pragma unroll
-    for (int off = 4; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-    // non-negative floats order like their bit patterns
-    if (lane == 0 && amax_bits != nullptr) atomicMax(amax_bits, __float_as_uint(mx));
+        for (int q = 0; q < 4; ++q) {
+          acc[2 * q] = round_bf16(acc[2 * q] + round_bf16(__fmul_rn(lo_f(yw[q]), wj)));
+          acc[2 * q + 1] = round_bf16(acc[2 * q + 1] + round_bf16(__fmul_rn(hi_f(yw[q]), wj)));
+        }
+      }
+      *reinterpret_cast<uint4 *>(out + t * width + (long long)v * 8) =
+          make_uint4(pack2(acc[0], acc[1]), pack2(acc[2], acc[3]), pack2(acc[4], acc[5]), pack2(acc[6], acc[7]));
+    }
   }
 }
 
@@ -224,15 +313,40 @@ cudaError_t run_scatter_add_scaled(void *out, const void *y, const long long *ro
 }
 
 cudaError_t run_swiglu_absmax(const void *gate_up, long long rows, int ffn, long long row_stride, void *h,
-                              unsigned int *amax_bits, cudaStream_t stream) {
+                              unsigned int *amax_bits, cudaStream_t stream, const int *unit_group, int groups) {
   if (amax_bits != nullptr) {
-    cudaError_t err = cudaMemsetAsync(amax_bits, 0, sizeof(unsigned int), stream);
+    cudaError_t err = cudaMemsetAsync(amax_bits, 0, sizeof(unsigned int) * (unit_group != nullptr ? groups : 1), stream);
     if (err != cudaSuccess) return err;
   }
   long long ctas = (long long)sm_count() * 8;
-  if (ctas > rows) ctas = rows;
+  const long long work = unit_group != nullptr ? (rows + kGroupedChunkRows - 1) / kGroupedChunkRows : rows;
+  if (ctas > work) ctas = work;
   swiglu_absmax_kernel<<<(unsigned)ctas, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(gate_up), rows, ffn,
-                                                            row_stride, static_cast<__nv_bfloat16 *>(h), amax_bits);
+                                                            row_stride, static_cast<__nv_bfloat16 *>(h), amax_bits, unit_group);
+  return cudaGetLastError();
+}
+
+cudaError_t run_abs_stats_grouped(const void *x, long long rows, int width, unsigned int *amax_bits, const int *unit_group,
+                                  int groups, cudaStream_t stream) {
+  cudaError_t err = cudaMemsetAsync(amax_bits, 0, sizeof(unsigned int) * groups, stream);
+  if (err != cudaSuccess) return err;
+  long long ctas = (long long)sm_count() * 8;
+  const long long work = (rows + kGroupedChunkRows - 1) / kGroupedChunkRows;
+  if (ctas > work) ctas = work;
+  abs_stats_grouped_kernel<<<(unsigned)ctas, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(x), rows, width, amax_bits,
+                                                                unit_group);
+  return cudaGetLastError();
+}
+
+cudaError_t run_moe_combine(void *out, const void *y, const int *dest, const long long *selected, const void *w,
+                            long long tokens, int top_k, int width, cudaStream_t stream) {
+  if (top_k < 1 || top_k > kCombineMaxTopK) return cudaErrorInvalidValue;
+  long long ctas = (long long)sm_count() * 8;
+  if (ctas > tokens) ctas = tokens;
+  if (ctas < 1) return cudaSuccess;
+  moe_combine_kernel<<<(unsigned)ctas, 256, 0, stream>>>(static_cast<__nv_bfloat16 *>(out), static_cast<const __nv_bfloat16 *>(y),
+                                                          dest, selected, static_cast<const __nv_bfloat16 *>(w), tokens, top_k,
+                                                          width);
   return cudaGetLastError();
 }
 

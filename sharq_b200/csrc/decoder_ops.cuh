@@ -11,8 +11,19 @@ cudaError_t run_rope_inplace(void *x, long long rows, long long row_stride, int 
 
 // h[rows, ffn] = silu(gate) * up from gate_up[rows, 2*ffn] (gate first); amax_bits (optional) is
 // zeroed and then raised to the bits of max|h|.
+// With unit_group (device, one int per 256 rows, < 0 = unit without rows) the rows are a grouped
+// activation: amax_bits has `groups` words, one per group, and rows of empty units are skipped.
 cudaError_t run_swiglu_absmax(const void *gate_up, long long rows, int ffn, long long row_stride, void *h,
-                              unsigned int *amax_bits, cudaStream_t stream);
+                              unsigned int *amax_bits, cudaStream_t stream, const int *unit_group = nullptr, int groups = 1);
+
+// max|x| per group of a grouped bf16 activation [rows, width] into amax_bits[groups] (zeroed first).
+cudaError_t run_abs_stats_grouped(const void *x, long long rows, int width, unsigned int *amax_bits, const int *unit_group,
+                                  int groups, cudaStream_t stream);
+
+// out[t, :] = sum over the top_k slots of token t, in ascending expert order, of y[dest[t, j], :] * w[t, j]
+// with bf16 roundings after every product and every addition (selected: expert index per slot).
+cudaError_t run_moe_combine(void *out, const void *y, const int *dest, const long long *selected, const void *w,
+                            long long tokens, int top_k, int width, cudaStream_t stream);
 
 // out[rows[i], :] += y[i, :] * w[i] in bf16 (distinct rows; width a multiple of 8).
 cudaError_t run_scatter_add_scaled(void *out, const void *y, const long long *rows, const void *w, long long n_rows,

@@ -109,6 +109,18 @@ struct GemmParams {
   int staged_store;  // output tiles are transposed through shared memory for coalesced stores (N % 8 == 0)
 };
 
+// Grouped launch (mixture-of-experts layers): the rows of the activation are sorted by group
+// (expert) in segments padded to whole 256-row units; every unit multiplies with the weight of
+// its own group.  unit_group[u] < 0 marks a unit without rows (skipped).
+constexpr int kMaxGroups = 16;
+struct GroupTable {
+  CUtensorMap tm_w[kMaxGroups];
+  const uint8_t *sfb_sparse[kMaxGroups];
+  const uint8_t *sfb_dense[kMaxGroups];
+  const int *unit_group;  // [units along M] on the device
+  const float *alpha;     // [groups] on the device: per-group factor (activation scale x weight scale)
+};
+
 // Epilogue of 32 accumulator columns held in registers: d = bf16(alpha * acc + beta * c_in),
 // then (+ bias) in bf16; rows >= M and columns >= N are masked.  A thread owns one row and
 // stores 64 contiguous bytes.
@@ -188,10 +200,9 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32
   }
 }
 
-template <int BN, bool SPARSE, bool DENSE, bool PAIR>
-__global__ void __launch_bounds__(kGemmThreads, 1)
-    gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a_dense,
-                const __grid_constant__ CUtensorMap tm_a_comp, const GemmParams p) {
+template <int BN, bool SPARSE, bool DENSE, bool PAIR, bool GROUPED>
+__device__ __forceinline__ void gemm_body(const CUtensorMap &tm_w, const CUtensorMap &tm_a_dense, const CUtensorMap &tm_a_comp,
+                                          const GemmParams &p, const GroupTable *gt) {
   using L = StageLayout<BN, SPARSE, DENSE, PAIR>;
   constexpr int S = L::kStages;
   constexpr int CG = PAIR ? 2 : 1;
@@ -230,7 +241,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
   if (threadIdx.x == 32) {
     // fetch the tensor maps while the barriers and tensor memory are being set up
-    ptx::tma_prefetch_desc(&tm_w);
+    if (!GROUPED) ptx::tma_prefetch_desc(&tm_w);
     if (DENSE) ptx::tma_prefetch_desc(&tm_a_dense);
     if (SPARSE) ptx::tma_prefetch_desc(&tm_a_comp);
   }
@@ -262,6 +273,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       bool ok = true;
       for (int u = unit0; u < num_units && ok; u += unit_stride) {
         const int tile = u / k_splits;
+        const int grp = GROUPED ? gt->unit_group[tile % m_units] : 0;
+        if (GROUPED && grp < 0) continue;
+        const CUtensorMap *tw = GROUPED ? &gt->tm_w[grp] : &tm_w;
+        const uint8_t *sfb_dense = GROUPED ? gt->sfb_dense[grp] : p.sfb_dense;
+        const uint8_t *sfb_sparse = GROUPED ? gt->sfb_sparse[grp] : p.sfb_sparse;
         const int m_tile = PAIR ? 2 * (tile % m_units) + (int)cta_rank : (tile % m_units);
         const int n_tile = tile / m_units;
         const int w_row = n_tile * BN + (PAIR ? (int)cta_rank * (BN / 2) : 0);
@@ -288,7 +304,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           uint32_t tx = L::kWBytes + L::kADenseBytes + L::kACompBytes + L::kEBytes;
           tx += (uint32_t)(n_sp * 512 * (1 + L::kBands) + n_d * 512 * (1 + L::kBands));
           ptx::mbar_arrive_expect_tx(full_bar + s, tx);
-          ptx::tma_load_2d(st + L::kOffW, &tm_w, it * 128, w_row, full_bar + s);
+          ptx::tma_load_2d(st + L::kOffW, tw, it * 128, w_row, full_bar + s);
           if (DENSE) {
             ptx::tma_load_2d(st + L::kOffADense, &tm_a_dense, it * 128, m_tile * kBM, full_bar + s);
             ptx::bulk_load_1d(st + L::kOffSfaD, p.sfa_dense + ((size_t)a_band * tiles_d + 4 * (size_t)it) * 512,
@@ -296,7 +312,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
             for (int b = 0; b < L::kBands; ++b)
               ptx::bulk_load_1d(st + L::kOffSfbD + b * 2048,
-                                p.sfb_dense + ((size_t)b_band[b] * tiles_d + 4 * (size_t)it) * 512,
+                                sfb_dense + ((size_t)b_band[b] * tiles_d + 4 * (size_t)it) * 512,
                                 (uint32_t)n_d * 512, full_bar + s);
           }
           if (SPARSE) {
@@ -308,7 +324,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
             for (int b = 0; b < L::kBands; ++b)
               ptx::bulk_load_1d(st + L::kOffSfbSp + b * 1024,
-                                p.sfb_sparse + ((size_t)b_band[b] * tiles_sp + 2 * (size_t)it) * 512,
+                                sfb_sparse + ((size_t)b_band[b] * tiles_sp + 2 * (size_t)it) * 512,
                                 (uint32_t)n_sp * 512, full_bar + s);
           }
         }
@@ -321,6 +337,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         uint32_t g = 0;
         bool ok = true;
         for (int u = unit0; u < num_units && ok; u += unit_stride) {
+          if (GROUPED && gt->unit_group[(u / k_splits) % m_units] < 0) continue;
           for (int it = k_begin(u), it_end = k_end(u); it < it_end; ++it, ++g) {
             const int s = (int)(g % S);
             if (!ptx::mbar_wait(full_bar + s, (g / S) & 1u, abort_flag)) {
@@ -339,7 +356,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         uint32_t g = 0;
         uint32_t tile_iter = 0;
         bool ok = true;
-        for (int u = unit0; u < num_units && ok; u += unit_stride, ++tile_iter) {
+        for (int u = unit0; u < num_units && ok; u += unit_stride) {
+          if (GROUPED && gt->unit_group[(u / k_splits) % m_units] < 0) continue;
           // the epilogue warps must have pulled the previous tile out of tensor memory
           const bool drained = PAIR ? ptx::mbar_wait_cluster(acc_empty_bar, (tile_iter & 1u) ^ 1u, abort_flag)
                                     : ptx::mbar_wait(acc_empty_bar, (tile_iter & 1u) ^ 1u, abort_flag);
@@ -432,6 +450,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             else
               ptx::tc_commit<1>(acc_full_bar);
           }
+          ++tile_iter;
         }
       }
     }
@@ -440,7 +459,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int ew = warp - 2;
     const int quad = warp & 3;  // tensor-memory lane quadrant this warp may read
     const int half = ew >> 2;   // which half of the tile's columns
-    const float alpha = p.alpha_ptr ? p.alpha * (*p.alpha_ptr) : p.alpha;
+    const float alpha0 = p.alpha_ptr ? p.alpha * (*p.alpha_ptr) : p.alpha;
     const float beta = p.beta;
     const bool has_c = (p.c_in != nullptr) && (beta != 0.0f);
     // Output path: a lane holds one row of the accumulator, so a direct store instruction would
@@ -450,11 +469,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // stored as 8 rows x 64 contiguous bytes per instruction.
     uint8_t *stage = p.staged_store ? smem + S * L::kStageBytes + 512 + ew * 2048 : nullptr;
     uint32_t tile_iter = 0;
-    for (int u = unit0; u < num_units; u += unit_stride, ++tile_iter) {
+    for (int u = unit0; u < num_units; u += unit_stride) {
       const int tile = u / k_splits;
+      const int grp = GROUPED ? gt->unit_group[tile % m_units] : 0;
+      if (GROUPED && grp < 0) continue;
+      const float alpha = GROUPED ? alpha0 * gt->alpha[grp] : alpha0;
       const int m_tile = PAIR ? 2 * (tile % m_units) + (int)cta_rank : (tile % m_units);
       const int n_tile = tile / m_units;
       bool ok = ptx::mbar_wait(acc_full_bar, tile_iter & 1u, abort_flag);
+      ++tile_iter;
       if (!ok) {
         *abort_flag = 1;
         atomicExch(p.error_flag, 3);
@@ -530,6 +553,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     ptx::tc_fence_after();
     ptx::tmem_dealloc<CG>(tmem_base, L::kTmemCols);
   }
+}
+
+template <int BN, bool SPARSE, bool DENSE, bool PAIR>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a_dense,
+                const __grid_constant__ CUtensorMap tm_a_comp, const GemmParams p) {
+  gemm_body<BN, SPARSE, DENSE, PAIR, false>(tm_w, tm_a_dense, tm_a_comp, p, nullptr);
+}
+
+// The fused SharQ GEMM of all groups (experts) of a mixture-of-experts layer in one launch, CTA pairs.
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_grouped_kernel(const __grid_constant__ GroupTable groups, const __grid_constant__ CUtensorMap tm_a_dense,
+                        const __grid_constant__ CUtensorMap tm_a_comp, const GemmParams p) {
+  gemm_body<256, true, true, true, true>(groups.tm_w[0], tm_a_dense, tm_a_comp, p, &groups);
 }
 
 // Second kernel of a split-K GEMM: the epilogue on the accumulated fp32 sums, 32 columns per thread.
@@ -705,6 +742,63 @@ cudaError_t launch(const GemmArgs &a, cudaStream_t stream) {
 }
 
 }  // namespace
+
+cudaError_t run_gemm_grouped(const GroupedGemmArgs &a, cudaStream_t stream) {
+  using L = StageLayout<256, true, true, true>;
+  static bool attr_set[64] = {};
+  if (a.groups < 1 || a.groups > kMaxGroups || a.m <= 0 || a.m % 256 != 0 || a.n <= 0 || a.k <= 0 || a.k % 128 != 0)
+    return cudaErrorInvalidValue;
+  int dev = 0, sms = 0;
+  cudaError_t e = device_info(&dev, &sms);
+  if (e != cudaSuccess) return e;
+  if (!attr_set[dev]) {
+    e = cudaFuncSetAttribute(gemm_grouped_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  GroupTable gt;
+  memset(&gt, 0, sizeof(gt));
+  for (int g = 0; g < a.groups; ++g) {
+    if (!make_tmap_bytes(&gt.tm_w[g], a.b[g], (uint64_t)a.n, (uint64_t)a.k / 2, L::kWRows, 128, CU_TENSOR_MAP_SWIZZLE_128B))
+      return cudaErrorInvalidValue;
+    gt.sfb_sparse[g] = static_cast<const uint8_t *>(a.sfb_sparse[g]);
+    gt.sfb_dense[g] = static_cast<const uint8_t *>(a.sfb_dense[g]);
+  }
+  gt.unit_group = a.unit_group;
+  gt.alpha = a.alpha_vec;
+  CUtensorMap tm_ad, tm_ac;
+  if (!make_tmap_bytes(&tm_ad, a.a_dense, (uint64_t)a.m, (uint64_t)a.k / 2, kBM, 128, CU_TENSOR_MAP_SWIZZLE_128B))
+    return cudaErrorInvalidValue;
+  if (!make_tmap_bytes(&tm_ac, a.a_comp, (uint64_t)a.m, (uint64_t)a.k / 4, kBM, 64, CU_TENSOR_MAP_SWIZZLE_64B))
+    return cudaErrorInvalidValue;
+  GemmParams p{};
+  p.staged_store = (a.n % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.d) & 15) == 0);
+  p.e = static_cast<const uint8_t *>(a.e);
+  p.sfa_sparse = static_cast<const uint8_t *>(a.sfa_sparse);
+  p.sfa_dense = static_cast<const uint8_t *>(a.sfa_dense);
+  p.d = static_cast<__nv_bfloat16 *>(a.d);
+  p.alpha = a.alpha;
+  p.m = a.m;
+  p.n = a.n;
+  p.k = a.k;
+  p.error_flag = a.error_flag;
+  p.k_splits = 1;
+  const int units = (a.m / 256) * ((a.n + 255) / 256);
+  const int clusters = units < sms / 2 ? units : sms / 2;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.gridDim = dim3(2 * clusters);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = L::kSmemBytes;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, gemm_grouped_kernel, gt, tm_ad, tm_ac, p);
+}
 
 cudaError_t run_gemm(const GemmArgs &a, cudaStream_t stream) {
   const bool sparse = a.a_comp != nullptr;

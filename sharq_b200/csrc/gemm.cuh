@@ -36,4 +36,23 @@ struct GemmArgs {
 
 cudaError_t run_gemm(const GemmArgs &args, cudaStream_t stream);
 
+// Fused SharQ GEMM over the groups (experts) of a mixture-of-experts layer in one launch.  The
+// activation rows are sorted by group, every group's segment padded to a multiple of 256 rows
+// (m is the padded total); unit_group[u] (device, m / 256 entries) is the group of rows
+// [256u, 256u + 256) or -1 for a unit without rows; row r of D is
+// alpha * alpha_vec[group] * (A_sparse[r] + A_res[r]) . W[group]^T.
+constexpr int kGemmMaxGroups = 16;
+struct GroupedGemmArgs {
+  const void *a_comp = nullptr, *e = nullptr, *sfa_sparse = nullptr, *a_dense = nullptr, *sfa_dense = nullptr;
+  int groups = 0;
+  const void *b[kGemmMaxGroups] = {}, *sfb_sparse[kGemmMaxGroups] = {}, *sfb_dense[kGemmMaxGroups] = {};
+  const int *unit_group = nullptr;
+  const float *alpha_vec = nullptr;
+  float alpha = 1.0f;
+  void *d = nullptr;
+  int m = 0, n = 0, k = 0;
+  int *error_flag = nullptr;
+};
+cudaError_t run_gemm_grouped(const GroupedGemmArgs &args, cudaStream_t stream);
+
 }  // namespace sharq

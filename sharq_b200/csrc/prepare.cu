@@ -207,6 +207,11 @@ struct PrepareParams {
   uint8_t *sf_res;
   int m, k;
   int row_tiles;  // ceil128(m) / 32
+  // grouped activation of a mixture-of-experts layer (mode 2, absmax ready): rows sorted by group in
+  // 256-row units; unit_group[u] < 0 = unit without rows; amax_bits and scale_vec_out have `groups` entries
+  const int *unit_group;
+  float *scale_vec_out;
+  int groups;
 };
 
 constexpr int kPrepareCtasPerSm = 3;
@@ -274,6 +279,8 @@ __global__ void __launch_bounds__(kPrepareThreads, kPrepareCtasPerSm) prepare_ke
     // reciprocal; clamp(min=1e-9) follows (kernels/src/bindings.cpp:337 of the reference).
     scale = fmaxf(__fmul_rn(amax, 1.0f / 2688.0f), 1.0e-9f);
     if (p.scale_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *p.scale_out = scale;
+    if (kMode == 2 && p.unit_group != nullptr && blockIdx.x == 0 && (int)threadIdx.x < p.groups)
+      p.scale_vec_out[threadIdx.x] = fmaxf(__fmul_rn(__uint_as_float(p.amax_bits[threadIdx.x]), 1.0f / 2688.0f), 1.0e-9f);
     if (kMode == 2) scale = round_to_bf16(scale);  // the divisor of the non-RMSNorm path, see round_to_bf16
     recip = __frcp_rn(scale);
   }
@@ -305,7 +312,14 @@ __global__ void __launch_bounds__(kPrepareThreads, kPrepareCtasPerSm) prepare_ke
     const int row = (tile / k_tiles) * kRowsPerCta + row_in_tile;
     const int group = k_tile * kGroupsPerWarp + group_in_tile;
     const bool col_ok = group < groups32;
-    const bool live = row < m && col_ok;
+    bool live = row < m && col_ok;
+    float t_scale = scale, t_recip = recip;
+    if (kMode == 2 && p.unit_group != nullptr) {  // per-group tensor scale; a 32-row tile lies inside one 256-row unit
+      const int grp = p.unit_group[((tile / k_tiles) * kRowsPerCta) >> 8];
+      live = live && grp >= 0;
+      t_scale = round_to_bf16(fmaxf(__fmul_rn(__uint_as_float(p.amax_bits[grp < 0 ? 0 : grp]), 1.0f / 2688.0f), 1.0e-9f));
+      t_recip = __frcp_rn(t_scale);
+    }
 
     uint32_t xw[16];
 #pragma unroll
@@ -342,7 +356,7 @@ __global__ void __launch_bounds__(kPrepareThreads, kPrepareCtasPerSm) prepare_ke
           }
         }
       }
-      scale_quantize_group<kMode, kDebug>(xw, scale, recip, tbl, o);
+      scale_quantize_group<kMode, kDebug>(xw, t_scale, t_recip, tbl, o);
 
       uint4 q = make_uint4(o.q_res[0], o.q_res[1], o.q_res[2], o.q_res[3]);
       *reinterpret_cast<uint4 *>(p.q_res + (size_t)row * (k / 2) + (size_t)group * 16) = q;
@@ -938,6 +952,27 @@ cudaError_t run_scaled_prepare(const void *x, const void *gamma, float eps, int 
   p.k = k;
   p.row_tiles = (m + 127) / 128 * 128 / kRowsPerCta;
   return launch_prepare(rms ? 1 : 2, false, p, stream);
+}
+
+cudaError_t run_grouped_prepare(const void *x, int m, int k, const unsigned int *amax_bits, const int *unit_group, int groups,
+                                void *a_comp, void *e, void *sfa_sparse, void *q_res, void *sf_res, float *scale_vec_out,
+                                cudaStream_t stream) {
+  if (m <= 0 || m % 256 != 0 || groups < 1) return cudaErrorInvalidValue;
+  PrepareParams p{};
+  p.x = static_cast<const __nv_bfloat16 *>(x);
+  p.amax_bits = amax_bits;
+  p.a_comp = static_cast<uint8_t *>(a_comp);
+  p.e = static_cast<uint8_t *>(e);
+  p.sfa_sparse = static_cast<uint8_t *>(sfa_sparse);
+  p.q_res = static_cast<uint8_t *>(q_res);
+  p.sf_res = static_cast<uint8_t *>(sf_res);
+  p.m = m;
+  p.k = k;
+  p.row_tiles = m / kRowsPerCta;
+  p.unit_group = unit_group;
+  p.scale_vec_out = scale_vec_out;
+  p.groups = groups;
+  return launch_prepare(2, false, p, stream);
 }
 
 }  // namespace sharq

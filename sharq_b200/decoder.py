@@ -80,6 +80,8 @@ class SharqDecoderLayer(torch.nn.Module):
         super().__init__()
         self.fused_glue = fused_glue
         self.reduce_hook = reduce_hook
+        self.grouped_experts = True   # mixture-of-experts FFN: grouped launches (False: the reference's per-expert loop)
+        self._expert_weight_scales = None
         if mode not in ("SHARQ", "NVFP4", "BF16"):
             raise ValueError(f"unknown mode {mode}")
         if mode != "SHARQ" and reduce_hook is not None:
@@ -262,6 +264,19 @@ class SharqDecoderLayer(torch.nn.Module):
         cfg = self.cfg
         m, h = hn.shape
         routing, selected = _route(hn, self.router, cfg.top_k)
+        if self.fused_glue and self.grouped_experts and hn.is_cuda:
+            out = self._moe_grouped(hn, routing, selected)
+            if self.reduce_hook is not None:
+                return self.reduce_hook(out)
+            if self.world > 1:
+                buf = tp.sum_buffer(None, hn.device, m * h * 2)
+                if buf is None:
+                    return tp.all_reduce_sum_(out)
+                slot, view = buf.take(m, h)
+                view.copy_(out)
+                buf.sum_(slot, m * h * 2)
+                return view
+            return out
         buf = tp.sum_buffer(None, hn.device, m * h * 2) if self.world > 1 and self.reduce_hook is None else None
         if buf is not None:
             slot, out = buf.take(m, h)
@@ -294,6 +309,49 @@ class SharqDecoderLayer(torch.nn.Module):
             else:
                 tp.all_reduce_sum_(out)
         return out
+
+    @torch.no_grad()
+    def _moe_grouped(self, hn: torch.Tensor, routing: torch.Tensor, selected: torch.Tensor) -> torch.Tensor:
+        """All experts in grouped launches with no host synchronisation (so the layer can be captured in a
+        CUDA graph): the token slots are sorted by expert on the device (ATen sort / cumsum: plumbing),
+        every expert's segment is padded to 256 rows, and gather -> prepare -> gate_up GEMM -> SwiGLU +
+        prepare -> down GEMM -> weighted combine each run once for all experts.  Same arithmetic per
+        token as the per-expert loop (each expert's rows get that expert's own tensor scales)."""
+        from . import ops
+
+        cfg = self.cfg
+        m, h = hn.shape
+        e, k = cfg.experts, cfg.top_k
+        dev = hn.device
+        slots = m * k
+        rows = ((slots + 255) // 256 + e) * 256  # upper bound of the padded segment lengths
+        flat = selected.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+        sorted_e = flat[order]
+        counts = torch.zeros(e, dtype=torch.int64, device=dev).scatter_add_(0, flat, torch.ones_like(flat))
+        padded = (counts + 255) // 256 * 256
+        ends = torch.cumsum(padded, 0)
+        starts = ends - padded
+        first = torch.cumsum(counts, 0) - counts
+        dest_sorted = starts[sorted_e] + (torch.arange(slots, device=dev) - first[sorted_e])
+        dest = torch.empty(slots, dtype=torch.int32, device=dev)
+        dest[order] = dest_sorted.to(torch.int32)
+        unit_starts = torch.arange(rows // 256, device=dev) * 256
+        unit_group = torch.searchsorted(ends, unit_starts, right=True)
+        unit_group = torch.where(unit_group < e, unit_group, torch.full_like(unit_group, -1)).to(torch.int32)
+        x_sorted = torch.zeros((rows, h), dtype=torch.bfloat16, device=dev)
+        x_sorted[dest_sorted] = hn[order // k]
+        w13 = [(g.weight_q, g.scale_w_sparse, g.scale_w_dense) for g, _ in self.experts]
+        w2 = [(d.weight_q, d.scale_w_sparse, d.scale_w_dense) for _, d in self.experts]
+        if self._expert_weight_scales is None:
+            self._expert_weight_scales = (torch.stack([g.weight_scale.reshape(()) for g, _ in self.experts]).float().contiguous(),
+                                          torch.stack([d.weight_scale.reshape(()) for _, d in self.experts]).float().contiguous())
+        ws13, ws2 = self._expert_weight_scales
+        p1 = ops.grouped_sparse_residual_quantize_x(x_sorted, unit_group, e)
+        gu = ops.linear_gemm_grouped(*p1[:5], w13, unit_group, (p1[5] * ws13).contiguous())
+        p2 = ops.grouped_swiglu_sparse_residual_quantize_x(gu, unit_group, e)
+        y = ops.linear_gemm_grouped(*p2[:5], w2, unit_group, (p2[5] * ws2).contiguous())
+        return ops.moe_combine(y, dest.view(m, k), selected.contiguous(), routing.contiguous())
 
     @torch.no_grad()
     def _forward_comparison_tp(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:

@@ -546,6 +546,91 @@ def sharq_linear_forward(x: torch.Tensor, qw: torch.Tensor, sfw_sparse: torch.Te
                              alpha_host=float(weight_scale))
 
 
+# --------------------------------------------------------------------------- grouped (mixture-of-experts) launches
+
+def _check_grouped(x: torch.Tensor, unit_group: torch.Tensor, groups: int, name: str):
+    _check(x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous(),
+           f"{name} must be a contiguous CUDA bfloat16 matrix")
+    _check(x.shape[0] % 256 == 0 and x.shape[0] > 0, "the grouped activation must have a positive multiple of 256 rows")
+    _check(unit_group.is_cuda and unit_group.dtype == torch.int32 and unit_group.is_contiguous()
+           and unit_group.numel() == x.shape[0] // 256, "unit_group must be a contiguous CUDA int32 vector with one entry per 256 rows")
+    _check(1 <= groups <= 16, "groups must be in [1, 16]")
+
+
+def grouped_sparse_residual_quantize_x(X: torch.Tensor, unit_group: torch.Tensor, groups: int, N: int = 0):
+    """Scaled prepare of a grouped activation (rows sorted by group in 256-row units, see
+    include/sharq_b200.h): -> (A_comp, E, SFA_sparse, Q_res, SF_res, scales [groups] float32), every group divided by
+    its own tensor scale."""
+    _check_grouped(X, unit_group, groups, "X")
+    M, K = int(X.shape[0]), int(X.shape[1])
+    _check(K % 128 == 0, f"K must be a multiple of 128, got {K}")
+    dev = X.device
+    A_comp, E, SFA, Q_res, SF_res, tail = _prepare_buffers(M, K, dev, extra=512)
+    amax = tail[:64]
+    scales = tail[256:256 + 4 * groups].view(torch.float32)
+    with _on_device(dev):
+        _lib.check(_lib.lib().sharq_grouped_sparse_residual_quantize_x(
+            _ptr(X), M, int(N), K, _ptr(unit_group), int(groups), _ptr(amax), _ptr(A_comp), _ptr(E), _ptr(SFA), _ptr(Q_res),
+            _ptr(SF_res), _ptr(scales), _stream(dev)))
+    return A_comp, E, SFA, Q_res, SF_res, scales
+
+
+def grouped_swiglu_sparse_residual_quantize_x(gate_up: torch.Tensor, unit_group: torch.Tensor, groups: int, N: int = 0):
+    """silu(gate) * up of a grouped merged activation [M, 2K] and the scaled prepare of the product per group:
+    -> (A_comp, E, SFA_sparse, Q_res, SF_res, scales [groups])."""
+    _check_grouped(gate_up, unit_group, groups, "gate_up")
+    M, K = int(gate_up.shape[0]), int(gate_up.shape[1]) // 2
+    _check(gate_up.shape[1] % 2 == 0 and K % 128 == 0, f"K must be a multiple of 128, got {K}")
+    dev = gate_up.device
+    A_comp, E, SFA, Q_res, SF_res, tail = _prepare_buffers(M, K, dev, extra=512 + M * K * 2)
+    amax = tail[:64]
+    scales = tail[256:256 + 4 * groups].view(torch.float32)
+    H = tail[512:512 + M * K * 2]
+    with _on_device(dev):
+        _lib.check(_lib.lib().sharq_grouped_swiglu_sparse_residual_quantize_x(
+            _ptr(gate_up), M, int(N), K, _ptr(H), _ptr(unit_group), int(groups), _ptr(amax), _ptr(A_comp), _ptr(E), _ptr(SFA),
+            _ptr(Q_res), _ptr(SF_res), _ptr(scales), _stream(dev)))
+    return A_comp, E, SFA, Q_res, SF_res, scales
+
+
+def linear_gemm_grouped(A_comp, E, SFA_sparse, Q_res, SF_res, weights, unit_group: torch.Tensor, alpha_vec: torch.Tensor,
+                        alpha: float = 1.0) -> torch.Tensor:
+    """Fused SharQ GEMM of a grouped activation against one weight per group in one launch.  weights: list of
+    (QW [N, K/2], SFW_sparse, SFW_dense), all of the same shape; alpha_vec: CUDA float32 [groups]."""
+    M, K = int(Q_res.shape[0]), int(Q_res.shape[1]) * 2
+    groups = len(weights)
+    N = int(weights[0][0].shape[0])
+    dev = Q_res.device
+    _check(M % 256 == 0, "the grouped activation must have a multiple of 256 rows")
+    _check(alpha_vec.is_cuda and alpha_vec.dtype == torch.float32 and alpha_vec.is_contiguous() and alpha_vec.numel() == groups,
+           "alpha_vec must be a contiguous CUDA float32 vector with one entry per group")
+    for qw, sfs, sfd in weights:
+        _check(tuple(qw.shape) == (N, K // 2) and qw.is_contiguous() and qw.device == dev, "weights must share one shape [N, K/2]")
+    arr = ctypes.c_void_p * groups
+    qws, sfss, sfds = (arr(*[w[i].data_ptr() for w in weights]) for i in range(3))
+    D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    with _on_device(dev):
+        _lib.check(_lib.lib().sharq_linear_gemm_grouped(
+            _ptr(A_comp), _ptr(E), _ptr(SFA_sparse), _ptr(Q_res), _ptr(SF_res), groups, qws, sfss, sfds, _ptr(unit_group),
+            _ptr(alpha_vec), float(alpha), M, N, K, _ptr(D), _ptr(_error_flag(dev)), _stream(dev)))
+    return D
+
+
+def moe_combine(y: torch.Tensor, dest: torch.Tensor, selected: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum over the top_k slots of token t, in ascending expert order, of y[dest[t, j]] * w[t, j] (bf16 roundings as
+    in the reference's index_add_ loop).  dest int32 [T, top_k], selected int64 [T, top_k], w bf16 [T, top_k]."""
+    T, top_k = int(selected.shape[0]), int(selected.shape[1])
+    _check(y.is_cuda and y.dtype == torch.bfloat16 and y.dim() == 2 and y.is_contiguous(), "y must be a contiguous CUDA bf16 matrix")
+    _check(dest.dtype == torch.int32 and dest.is_contiguous() and dest.numel() == T * top_k, "dest must be int32 [T, top_k]")
+    _check(selected.dtype == torch.int64 and selected.is_contiguous(), "selected must be contiguous int64 [T, top_k]")
+    _check(w.dtype == torch.bfloat16 and w.is_contiguous() and w.numel() == T * top_k, "w must be contiguous bf16 [T, top_k]")
+    out = torch.empty((T, int(y.shape[1])), dtype=torch.bfloat16, device=y.device)
+    with _on_device(y.device):
+        _lib.check(_lib.lib().sharq_moe_combine(_ptr(out), _ptr(y), _ptr(dest), _ptr(selected), _ptr(w), T, top_k,
+                                                int(y.shape[1]), _stream(y.device)))
+    return out
+
+
 def set_gemm_tile_n(tile_n: int) -> None:
     """Force the GEMM tile width (0 = automatic, 128 or 256); test/tuning hook."""
     _lib.check(_lib.lib().sharq_set_gemm_tile_n(int(tile_n)))

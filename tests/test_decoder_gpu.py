@@ -58,6 +58,55 @@ def test_small_moe_decoder_tracks_bf16_reference():
     assert torch.equal(got, plain)  # SwiGLU fused into the w2 prepare changes no bit
 
 
+@pytest.mark.parametrize("tokens", [384, 1000])
+def test_grouped_experts_equal_the_per_expert_loop(tokens):
+    """One grouped launch per step over all experts (sorted token slots, per-expert tensor scales, grouped
+    GEMMs, ordered combine) gives the bits of the reference-style per-expert loop, and the layer can be
+    captured in a CUDA graph (no host synchronisation)."""
+    from sharq_b200 import ops
+    from sharq_b200.decoder import DecoderConfig, SharqDecoder
+
+    cfg = DecoderConfig(hidden=512, layers=1, heads=4, kv_heads=2, head_dim=128, ffn=1024, vocab=2000, experts=4, top_k=2)
+    model = SharqDecoder(cfg, torch.device("cuda"), seed=9)
+    layer = model.layers[0]
+    hn = torch.randn(tokens, cfg.hidden, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).cuda()
+    hn[:, 7] *= 20
+    layer.grouped_experts = False
+    loop = layer._moe(hn).clone()
+    layer.grouped_experts = True
+    grouped = layer._moe(hn).clone()
+    ops.check_device_errors()
+    assert torch.isfinite(grouped).all()
+    assert torch.equal(grouped, loop), float((grouped.float() - loop.float()).abs().max())
+    # a skewed routing: every token to experts 1 and 3 (experts 0 and 2 get no rows)
+    saved = layer.router.clone()
+    layer.router.zero_()
+    layer.router[1] = 1.0
+    layer.router[3] = 0.5
+    hn_pos = hn.abs()
+    layer.grouped_experts = False
+    loop = layer._moe(hn_pos).clone()
+    layer.grouped_experts = True
+    grouped = layer._moe(hn_pos).clone()
+    assert torch.equal(grouped, loop)
+    layer.router.copy_(saved)
+    # graph capture
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        layer._moe(hn)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        out = layer._moe(hn)
+    g.replay()
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+    layer.grouped_experts = False
+    assert torch.equal(out, layer._moe(hn))
+
+
 @pytest.mark.parametrize("world", [4, 8])
 def test_padded_tensor_parallel_layout_matches_single_rank(world):
     """A Qwen-like shape that does not divide (7 query heads on 1 KV head, FFN 1920): the KV
