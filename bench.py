@@ -492,8 +492,8 @@ def run_ours(args):
         barrier()
         ops.check_device_errors()
         pg = None
-        # the expert loop of a mixture-of-experts layer has data-dependent shapes: eager only
-        if not args.no_graph and pcfg.experts == 0:
+        # (mixture-of-experts layers run as grouped launches without host synchronisation, so they capture too)
+        if not args.no_graph:
             pg = torch.cuda.CUDAGraph()
             with torch.cuda.graph(pg):
                 logits = model.prefill(ids)

@@ -243,7 +243,8 @@ int sharq_allreduce_bf16_peer(void *const *rank_data_ptrs, void *const *rank_fla
  * of rows [256u, 256u+256) or < 0 for a unit without rows.  Arithmetic per row is that of the
  * per-expert calls: every expert's rows are divided by that expert's own tensor scale.
  *   sharq_grouped_sparse_residual_quantize_x: per-expert max|X| (into amax_workspace, `groups`
- *     uint32 words) + scaled prepare; scale_vec_out[g] = clamp(amax_g / 2688, 1e-9).
+ *     uint32 words) + scaled prepare; scale_vec_out[g] = clamp(amax_g / 2688, 1e-9).  src_row (optional,
+ *     device, M ints) gathers: grouped row r is row src_row[r] of the token-major X (< 0: padding row).
  *   sharq_grouped_swiglu_sparse_residual_quantize_x: H = silu(gate) * up of gate_up [M, 2K] (written
  *     to h_bf16 [M, K]), per-expert max|H| and the scaled prepare of H.
  *   sharq_linear_gemm_grouped: D[r] = alpha * alpha_vec[g] * (A_sparse[r] + A_res[r]) . W_g^T for every
@@ -252,9 +253,9 @@ int sharq_allreduce_bf16_peer(void *const *rank_data_ptrs, void *const *rank_fla
  *   sharq_moe_combine: out[t] = sum over the top_k slots of token t, in ascending expert order, of
  *     y[dest[t,j]] * w[t,j] with bf16 rounding after every product and addition, which is what the
  *     reference's sequence of index_add_ calls on a zero buffer computes. */
-int sharq_grouped_sparse_residual_quantize_x(const void *x_bf16, int m, int n, int k, const int *unit_group, int groups,
-                                            void *amax_workspace, void *a_comp, void *e, void *sfa_sparse, void *q_res,
-                                            void *sf_res, float *scale_vec_out, void *stream);
+int sharq_grouped_sparse_residual_quantize_x(const void *x_bf16, const int *src_row, int m, int n, int k,
+                                            const int *unit_group, int groups, void *amax_workspace, void *a_comp, void *e,
+                                            void *sfa_sparse, void *q_res, void *sf_res, float *scale_vec_out, void *stream);
 int sharq_grouped_swiglu_sparse_residual_quantize_x(const void *gate_up_bf16, int m, int n, int k, void *h_bf16,
                                                    const int *unit_group, int groups, void *amax_workspace, void *a_comp,
                                                    void *e, void *sfa_sparse, void *q_res, void *sf_res,

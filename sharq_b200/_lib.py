@@ -54,7 +54,7 @@ SIGNATURES = {
     "sharq_allreduce_bf16_multimem": (c_int, [_P, POINTER(c_void_p), c_int, c_int, c_size_t, c_int, _P, _P]),
     "sharq_allreduce_flag_bytes": (c_size_t, []),
     "sharq_allreduce_bf16_peer": (c_int, [POINTER(c_void_p), POINTER(c_void_p), c_int, c_int, c_size_t, c_int, _P, _P]),
-    "sharq_grouped_sparse_residual_quantize_x": (c_int, [_P, c_int, c_int, c_int, _P, c_int, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "sharq_grouped_sparse_residual_quantize_x": (c_int, [_P, _P, c_int, c_int, c_int, _P, c_int, _P, _P, _P, _P, _P, _P, _P, _P]),
     "sharq_grouped_swiglu_sparse_residual_quantize_x": (
         c_int, [_P, c_int, c_int, c_int, _P, _P, c_int, _P, _P, _P, _P, _P, _P, _P, _P]),
     "sharq_linear_gemm_grouped": (

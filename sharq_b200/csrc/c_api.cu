@@ -255,19 +255,20 @@ int sharq_allreduce_bf16_peer(void *const *rank_data_ptrs, void *const *rank_fla
                     "allreduce_peer launch");
 }
 
-int sharq_grouped_sparse_residual_quantize_x(const void *x_bf16, int m, int n, int k, const int *unit_group, int groups,
-                                            void *amax_workspace, void *a_comp, void *e, void *sfa_sparse, void *q_res,
-                                            void *sf_res, float *scale_vec_out, void *stream) {
+int sharq_grouped_sparse_residual_quantize_x(const void *x_bf16, const int *src_row, int m, int n, int k,
+                                            const int *unit_group, int groups, void *amax_workspace, void *a_comp, void *e,
+                                            void *sfa_sparse, void *q_res, void *sf_res, float *scale_vec_out, void *stream) {
   (void)n;
   SHARQ_REQUIRE(m > 0 && m % 256 == 0 && k > 0 && k % 128 == 0, "M must be a positive multiple of 256 and K of 128");
   SHARQ_REQUIRE(groups >= 1 && groups <= sharq::kGemmMaxGroups, "groups must be in [1, %d]", sharq::kGemmMaxGroups);
   SHARQ_REQUIRE(x_bf16 && unit_group && amax_workspace && a_comp && e && sfa_sparse && q_res && sf_res && scale_vec_out,
                 "null buffer");
   auto *amax = static_cast<unsigned int *>(amax_workspace);
-  if (check_cuda(sharq::run_abs_stats_grouped(x_bf16, m, k, amax, unit_group, groups, as_stream(stream)), "grouped absmax"))
+  if (check_cuda(sharq::run_abs_stats_grouped(x_bf16, m, k, amax, unit_group, groups, as_stream(stream), src_row),
+                 "grouped absmax"))
     return 1;
   return check_cuda(sharq::run_grouped_prepare(x_bf16, m, k, amax, unit_group, groups, a_comp, e, sfa_sparse, q_res, sf_res,
-                                               scale_vec_out, as_stream(stream)),
+                                               scale_vec_out, as_stream(stream), src_row),
                     "grouped_sparse_residual_quantize_x");
 }
 

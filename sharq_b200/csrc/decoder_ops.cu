@@ -185,7 +185,8 @@ __global__ void __launch_bounds__(256) swiglu_absmax_kernel(const __nv_bfloat16 
 // Tensor absmax per group of a grouped bf16 activation [rows, width] (see swiglu_absmax_kernel).
 __global__ void __launch_bounds__(256) abs_stats_grouped_kernel(const __nv_bfloat16 *__restrict__ x, long long rows, int width,
                                                                 unsigned int *__restrict__ amax_bits,
-                                                                const int *__restrict__ unit_group) {
+                                                                const int *__restrict__ unit_group,
+                                                                const int *__restrict__ src_row) {
   __shared__ float warp_max[8];
   const int vecs = width >> 3;
   const long long n_chunks = (rows + kGroupedChunkRows - 1) / kGroupedChunkRows;
@@ -194,10 +195,12 @@ __global__ void __launch_bounds__(256) abs_stats_grouped_kernel(const __nv_bfloa
     const int grp = unit_group[row_lo / 256];
     if (grp < 0) continue;
     __nv_bfloat162 mx2 = __floats2bfloat162_rn(0.0f, 0.0f);
-    const uint4 *src = reinterpret_cast<const uint4 *>(x + row_lo * width);
     const long long n16 = (row_hi - row_lo) * vecs;
     for (long long i = threadIdx.x; i < n16; i += blockDim.x) {
-      const uint4 v = __ldg(src + i);
+      const long long r = row_lo + i / vecs;
+      const long long in_row = src_row != nullptr ? src_row[r] : r;  // gathered rows; < 0: a padding row
+      if (in_row < 0) continue;
+      const uint4 v = __ldg(reinterpret_cast<const uint4 *>(x + in_row * width) + (i % vecs));
       mx2 = __hmax2(mx2, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&v.x)));
       mx2 = __hmax2(mx2, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&v.y)));
       mx2 = __hmax2(mx2, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&v.z)));
@@ -327,14 +330,14 @@ cudaError_t run_swiglu_absmax(const void *gate_up, long long rows, int ffn, long
 }
 
 cudaError_t run_abs_stats_grouped(const void *x, long long rows, int width, unsigned int *amax_bits, const int *unit_group,
-                                  int groups, cudaStream_t stream) {
+                                  int groups, cudaStream_t stream, const int *src_row) {
   cudaError_t err = cudaMemsetAsync(amax_bits, 0, sizeof(unsigned int) * groups, stream);
   if (err != cudaSuccess) return err;
   long long ctas = (long long)sm_count() * 8;
   const long long work = (rows + kGroupedChunkRows - 1) / kGroupedChunkRows;
   if (ctas > work) ctas = work;
   abs_stats_grouped_kernel<<<(unsigned)ctas, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(x), rows, width, amax_bits,
-                                                                unit_group);
+                                                                unit_group, src_row);
   return cudaGetLastError();
 }
 

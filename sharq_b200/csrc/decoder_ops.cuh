@@ -17,8 +17,9 @@ cudaError_t run_swiglu_absmax(const void *gate_up, long long rows, int ffn, long
                               unsigned int *amax_bits, cudaStream_t stream, const int *unit_group = nullptr, int groups = 1);
 
 // max|x| per group of a grouped bf16 activation [rows, width] into amax_bits[groups] (zeroed first).
+// With src_row, grouped row r is input row src_row[r] of x (< 0: a padding row without data).
 cudaError_t run_abs_stats_grouped(const void *x, long long rows, int width, unsigned int *amax_bits, const int *unit_group,
-                                  int groups, cudaStream_t stream);
+                                  int groups, cudaStream_t stream, const int *src_row = nullptr);
 
 // out[t, :] = sum over the top_k slots of token t, in ascending expert order, of y[dest[t, j], :] * w[t, j]
 // with bf16 roundings after every product and every addition (selected: expert index per slot).

@@ -212,6 +212,7 @@ struct PrepareParams {
   const int *unit_group;
   float *scale_vec_out;
   int groups;
+  const int *src_row;  // optional gather: output row r is prepared from input row src_row[r] (< 0: a padding row of zeros)
 };
 
 constexpr int kPrepareCtasPerSm = 3;
@@ -295,13 +296,19 @@ __global__ void __launch_bounds__(kPrepareThreads, kPrepareCtasPerSm) prepare_ke
   // before the current tile is processed, so the loads overlap the arithmetic
   uint4 next[4];
   float next_inv = 0.0f;
+  bool next_row_ok = true;
   auto issue_loads = [&](int tile) {
     const int row = (tile / k_tiles) * kRowsPerCta + row_in_tile;
     const int group = (tile % k_tiles) * kGroupsPerWarp + group_in_tile;
     if (tile < total_tiles && row < m && group < groups32) {
-      const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (size_t)row * k + (size_t)group * 32);
+      int in_row = row;
+      if (kMode == 2 && p.src_row != nullptr) in_row = p.src_row[row];
+      next_row_ok = in_row >= 0;
+      if (in_row >= 0) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (size_t)in_row * k + (size_t)group * 32);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) next[j] = __ldg(src + j);
+        for (int j = 0; j < 4; ++j) next[j] = __ldg(src + j);
+      }
       if (kMode == 1) next_inv = p.inv_rms[row];
     }
   };
@@ -330,6 +337,7 @@ __global__ void __launch_bounds__(kPrepareThreads, kPrepareCtasPerSm) prepare_ke
       xw[4 * j + 3] = next[j].w;
     }
     const float inv = next_inv;
+    live = live && next_row_ok;
     issue_loads(tile + gridDim.x);
 
     GroupOut o;
@@ -956,7 +964,7 @@ cudaError_t run_scaled_prepare(const void *x, const void *gamma, float eps, int 
 
 cudaError_t run_grouped_prepare(const void *x, int m, int k, const unsigned int *amax_bits, const int *unit_group, int groups,
                                 void *a_comp, void *e, void *sfa_sparse, void *q_res, void *sf_res, float *scale_vec_out,
-                                cudaStream_t stream) {
+                                cudaStream_t stream, const int *src_row) {
   if (m <= 0 || m % 256 != 0 || groups < 1) return cudaErrorInvalidValue;
   PrepareParams p{};
   p.x = static_cast<const __nv_bfloat16 *>(x);
@@ -972,6 +980,7 @@ cudaError_t run_grouped_prepare(const void *x, int m, int k, const unsigned int 
   p.unit_group = unit_group;
   p.scale_vec_out = scale_vec_out;
   p.groups = groups;
+  p.src_row = src_row;
   return launch_prepare(2, false, p, stream);
 }
 

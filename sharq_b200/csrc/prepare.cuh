@@ -27,11 +27,12 @@ cudaError_t run_scaled_prepare(const void *x, const void *gamma, float eps, int 
 // Tensor-scale prepare of a grouped activation (mixture-of-experts layers): rows sorted by group in
 // 256-row units (m a multiple of 256), unit_group[u] < 0 = unit without rows (its outputs are
 // zero metadata / scales and untouched payload), amax_bits[g] = bits of max|x| over group g
-// (already computed), scale_vec_out[g] = clamp(amax_g / 2688, 1e-9).  Every group is divided by
+// (already computed), scale_vec_out[g] = clamp(amax_g / 2688, 1e-9).  With src_row the output row r is
+// prepared from input row src_row[r] of x (a gather; < 0: a padding row, all-zero scales).  Every group is divided by
 // its own scale, exactly as a separate call per group would do.
 cudaError_t run_grouped_prepare(const void *x, int m, int k, const unsigned int *amax_bits, const int *unit_group, int groups,
                                 void *a_comp, void *e, void *sfa_sparse, void *q_res, void *sf_res, float *scale_vec_out,
-                                cudaStream_t stream);
+                                cudaStream_t stream, const int *src_row = nullptr);
 
 // Grid barriers of the one-launch prepare that ran out on the current device since the library
 // was loaded (0 in a healthy process; -1 when the counter cannot be read).

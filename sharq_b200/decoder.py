@@ -339,15 +339,15 @@ class SharqDecoderLayer(torch.nn.Module):
         unit_starts = torch.arange(rows // 256, device=dev) * 256
         unit_group = torch.searchsorted(ends, unit_starts, right=True)
         unit_group = torch.where(unit_group < e, unit_group, torch.full_like(unit_group, -1)).to(torch.int32)
-        x_sorted = torch.zeros((rows, h), dtype=torch.bfloat16, device=dev)
-        x_sorted[dest_sorted] = hn[order // k]
+        src_row = torch.full((rows,), -1, dtype=torch.int32, device=dev)  # token of every grouped row, -1 = padding
+        src_row[dest_sorted] = (order // k).to(torch.int32)
         w13 = [(g.weight_q, g.scale_w_sparse, g.scale_w_dense) for g, _ in self.experts]
         w2 = [(d.weight_q, d.scale_w_sparse, d.scale_w_dense) for _, d in self.experts]
         if self._expert_weight_scales is None:
             self._expert_weight_scales = (torch.stack([g.weight_scale.reshape(()) for g, _ in self.experts]).float().contiguous(),
                                           torch.stack([d.weight_scale.reshape(()) for _, d in self.experts]).float().contiguous())
         ws13, ws2 = self._expert_weight_scales
-        p1 = ops.grouped_sparse_residual_quantize_x(x_sorted, unit_group, e)
+        p1 = ops.grouped_sparse_residual_quantize_x(hn.contiguous(), unit_group, e, src_row=src_row)
         gu = ops.linear_gemm_grouped(*p1[:5], w13, unit_group, (p1[5] * ws13).contiguous())
         p2 = ops.grouped_swiglu_sparse_residual_quantize_x(gu, unit_group, e)
         y = ops.linear_gemm_grouped(*p2[:5], w2, unit_group, (p2[5] * ws2).contiguous())

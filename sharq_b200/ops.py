@@ -557,12 +557,23 @@ def _check_grouped(x: torch.Tensor, unit_group: torch.Tensor, groups: int, name:
     _check(1 <= groups <= 16, "groups must be in [1, 16]")
 
 
-def grouped_sparse_residual_quantize_x(X: torch.Tensor, unit_group: torch.Tensor, groups: int, N: int = 0):
+def grouped_sparse_residual_quantize_x(X: torch.Tensor, unit_group: torch.Tensor, groups: int, N: int = 0,
+                                       src_row: Optional[torch.Tensor] = None):
     """Scaled prepare of a grouped activation (rows sorted by group in 256-row units, see
     include/sharq_b200.h): -> (A_comp, E, SFA_sparse, Q_res, SF_res, scales [groups] float32), every group divided by
-    its own tensor scale."""
-    _check_grouped(X, unit_group, groups, "X")
-    M, K = int(X.shape[0]), int(X.shape[1])
+    its own tensor scale.  With src_row (int32, one entry per grouped row, < 0 = padding) X is the token-major
+    activation and grouped row r is X[src_row[r]]."""
+    if src_row is None:
+        _check_grouped(X, unit_group, groups, "X")
+        M = int(X.shape[0])
+    else:
+        _check(X.is_cuda and X.dtype == torch.bfloat16 and X.dim() == 2 and X.is_contiguous(),
+               "X must be a contiguous CUDA bfloat16 matrix")
+        _check(src_row.is_cuda and src_row.dtype == torch.int32 and src_row.is_contiguous(), "src_row must be contiguous CUDA int32")
+        M = int(src_row.numel())
+        _check(M % 256 == 0 and unit_group.numel() == M // 256 and unit_group.dtype == torch.int32,
+               "src_row must have a multiple of 256 entries and unit_group one int32 per 256")
+    K = int(X.shape[1])
     _check(K % 128 == 0, f"K must be a multiple of 128, got {K}")
     dev = X.device
     A_comp, E, SFA, Q_res, SF_res, tail = _prepare_buffers(M, K, dev, extra=512)
@@ -570,7 +581,7 @@ def grouped_sparse_residual_quantize_x(X: torch.Tensor, unit_group: torch.Tensor
     scales = tail[256:256 + 4 * groups].view(torch.float32)
     with _on_device(dev):
         _lib.check(_lib.lib().sharq_grouped_sparse_residual_quantize_x(
-            _ptr(X), M, int(N), K, _ptr(unit_group), int(groups), _ptr(amax), _ptr(A_comp), _ptr(E), _ptr(SFA), _ptr(Q_res),
+            _ptr(X), _ptr(src_row), M, int(N), K, _ptr(unit_group), int(groups), _ptr(amax), _ptr(A_comp), _ptr(E), _ptr(SFA), _ptr(Q_res),
             _ptr(SF_res), _ptr(scales), _stream(dev)))
     return A_comp, E, SFA, Q_res, SF_res, scales
 
