@@ -1,17 +1,19 @@
 """Benchmark of the SharQ quantized-linear hot path on B200.
 
     python bench.py --gpus N --steps K --warmup W            # this project's CUDA path
-    python bench.py --impl reference --gpus N --steps K ...  # SHARQ_SIM CPU path (rank 0 only)
+    python bench.py --impl reference --gpus N --steps K ...  # the reference's SHARQ_SIM CPU path (rank 0 only)
 
-Workload (config.workload): the linear layers of a Llama-3-8B-shaped decoder at M tokens
-(default 2048 = batch 1 x seqlen 2048): per layer qkv 6144x4096 and gate_up 28672x4096
-(RMSNorm-fused prepare + fused sparse/residual GEMM), o_proj 4096x4096 and down
-4096x14336 (scaled prepare + GEMM), with config-0 value distributions (X ~ N(0,1) with 1%
-of channels x20, gamma ~ 1+N(0,0.1), W ~ N(0,0.02)).  One step runs all `--layers`
-(default 32) layers, each with its own weights, so the inputs of a step (3.5 GB of packed
-weights) are far larger than L2.  With N > 1 GPUs the layers are tensor-parallel
-(qkv/gate_up column-parallel, o/down row-parallel + NCCL all-reduce); the total work is
-fixed (strong scaling).
+Workload (config.workload): the linear path of a Llama-3-8B-shaped decoder at M tokens (default
+2048 = batch 1 x seqlen 2048), one chain per step over `--layers` (default 32) layers, each with its
+own weights: RMSNorm prepare -> qkv 6144x4096; prepare -> o_proj 4096x4096 -> residual add + RMSNorm
+prepare -> gate_up 28672x4096; prepare -> down 4096x14336 -> residual add + RMSNorm prepare of the next
+layer.  The attention and SwiGLU outputs that feed o_proj and down are fixed inputs; value
+distributions are config 0's (X ~ N(0,1) with 1% of channels x20, gamma ~ 1+N(0,0.1), W ~ N(0,0.02)).
+The inputs of a step (3.5 GB of packed weights) are far larger than L2.  With N > 1 GPUs the layers
+are tensor-parallel (qkv/gate_up column-parallel, o/down row-parallel), the residual stream is sharded
+by rows and one kernel per GPU does reduce-scatter + residual add + RMSNorm prepare + all-gather of the
+packed activation (--tp-mode allreduce: replicated residual stream and an all-reduce kernel instead);
+the total work is fixed (strong scaling).
 
 metric: dense-equivalent linear throughput, sum(2*M*N*K) / time, in TFLOP/s.
 One JSON line is printed by rank 0.
