@@ -323,24 +323,7 @@ class SharqDecoderLayer(torch.nn.Module):
         m, h = hn.shape
         e, k = cfg.experts, cfg.top_k
         dev = hn.device
-        slots = m * k
-        rows = ((slots + 255) // 256 + e) * 256  # upper bound of the padded segment lengths
-        flat = selected.reshape(-1)
-        order = torch.argsort(flat, stable=True)
-        sorted_e = flat[order]
-        counts = torch.zeros(e, dtype=torch.int64, device=dev).scatter_add_(0, flat, torch.ones_like(flat))
-        padded = (counts + 255) // 256 * 256
-        ends = torch.cumsum(padded, 0)
-        starts = ends - padded
-        first = torch.cumsum(counts, 0) - counts
-        dest_sorted = starts[sorted_e] + (torch.arange(slots, device=dev) - first[sorted_e])
-        dest = torch.empty(slots, dtype=torch.int32, device=dev)
-        dest[order] = dest_sorted.to(torch.int32)
-        unit_starts = torch.arange(rows // 256, device=dev) * 256
-        unit_group = torch.searchsorted(ends, unit_starts, right=True)
-        unit_group = torch.where(unit_group < e, unit_group, torch.full_like(unit_group, -1)).to(torch.int32)
-        src_row = torch.full((rows,), -1, dtype=torch.int32, device=dev)  # token of every grouped row, -1 = padding
-        src_row[dest_sorted] = (order // k).to(torch.int32)
+        dest, src_row, unit_group = moe_grouping(selected, e)
         w13 = [(g.weight_q, g.scale_w_sparse, g.scale_w_dense) for g, _ in self.experts]
         w2 = [(d.weight_q, d.scale_w_sparse, d.scale_w_dense) for _, d in self.experts]
         if self._expert_weight_scales is None:
@@ -351,7 +334,7 @@ class SharqDecoderLayer(torch.nn.Module):
         gu = ops.linear_gemm_grouped(*p1[:5], w13, unit_group, (p1[5] * ws13).contiguous())
         p2 = ops.grouped_swiglu_sparse_residual_quantize_x(gu, unit_group, e)
         y = ops.linear_gemm_grouped(*p2[:5], w2, unit_group, (p2[5] * ws2).contiguous())
-        return ops.moe_combine(y, dest.view(m, k), selected.contiguous(), routing.contiguous())
+        return ops.moe_combine(y, dest, selected.contiguous(), routing.contiguous())
 
     @torch.no_grad()
     def _forward_comparison_tp(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
@@ -451,6 +434,37 @@ class SharqDecoderLayer(torch.nn.Module):
             hmid = F.silu(F.linear(y, r["gate"])) * F.linear(y, r["up"])
         x2 = x2 + F.linear(hmid, r["down"])
         return x2.view(b, s, h)
+
+
+def moe_grouping(selected: torch.Tensor, experts: int, unit: int = 256):
+    """Device-side plan of a grouped mixture-of-experts step, without host synchronisation.
+    selected [tokens, top_k] (expert of every token slot) ->
+      dest       int32 [tokens, top_k]: row of every slot in the grouped activation (slots sorted by expert,
+                 ascending token order inside an expert, every expert's segment padded to a multiple of `unit` rows)
+      src_row    int32 [rows]: token of every grouped row, -1 for padding rows
+      unit_group int32 [rows / unit]: expert of every unit, -1 for units without rows
+    rows = (ceil(tokens * top_k / unit) + experts) * unit is the static upper bound of the padded total."""
+    tokens, k = selected.shape
+    dev = selected.device
+    slots = tokens * k
+    rows = ((slots + unit - 1) // unit + experts) * unit
+    flat = selected.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    sorted_e = flat[order]
+    counts = torch.zeros(experts, dtype=torch.int64, device=dev).scatter_add_(0, flat, torch.ones_like(flat))
+    padded = (counts + unit - 1) // unit * unit
+    ends = torch.cumsum(padded, 0)
+    starts = ends - padded
+    first = torch.cumsum(counts, 0) - counts
+    dest_sorted = starts[sorted_e] + (torch.arange(slots, device=dev) - first[sorted_e])
+    dest = torch.empty(slots, dtype=torch.int32, device=dev)
+    dest[order] = dest_sorted.to(torch.int32)
+    src_row = torch.full((rows,), -1, dtype=torch.int32, device=dev)
+    src_row[dest_sorted] = (order // k).to(torch.int32)
+    unit_starts = torch.arange(rows // unit, device=dev) * unit
+    unit_group = torch.searchsorted(ends, unit_starts, right=True)
+    unit_group = torch.where(unit_group < experts, unit_group, torch.full_like(unit_group, -1)).to(torch.int32)
+    return dest.view(tokens, k), src_row, unit_group
 
 
 def _rmsnorm(t: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
