@@ -9,7 +9,7 @@
 // them exactly as the single-GPU RMSNorm prepare does (same per-row inv_rms, same tensor scale,
 // hence the same bytes), and pushes the packed result (A_comp, E, both scale buffers, Q_res:
 // 0.906 bytes per element instead of 2 for bf16) into every GPU's copy of the prepared
-// activation (multimem.st, as the words are produced).  Compared with "all-reduce, then every GPU prepares all M rows"
+// activation (multimem.st).  Compared with "all-reduce, then every GPU prepares all M rows"
 // a GPU receives 1/world + 0.45 of the bf16 activation instead of all of it, and prepares
 // M / world rows instead of M.
 //
@@ -23,7 +23,7 @@
 //      precedes it on the stream); all CTAs wait for all GPUs before the first reduce.
 //   B  tensor absmax: after a grid-wide barrier CTA 0 stores {absmax, launch number} as one
 //      8-byte word into every GPU's state; all CTAs wait until all words carry the number.
-//   C  "broadcast landed": after all its CTAs have fenced their multicast stores, a GPU signals all
+//   C  "broadcast landed": after its packed rows are stored to all GPUs, a GPU signals all
 //      others; CTA 0 waits for all of them before the kernel ends, so the GEMM that follows on
 //      the stream reads complete buffers.
 // Every wait is bounded (about ten seconds); a wait that runs out sets *error_flag and the
@@ -89,14 +89,6 @@ __device__ __forceinline__ void st_multicast_16(uint8_t *mc_addr, const uint4 &v
                : "memory");
 }
 
-__device__ __forceinline__ void st_multicast_8(uint8_t *mc_addr, uint32_t a, uint32_t b) {
-  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(mc_addr), "r"(a), "r"(b) : "memory");
-}
-
-__device__ __forceinline__ void st_multicast_4(uint8_t *mc_addr, uint32_t a) {
-  asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(mc_addr), "r"(a) : "memory");
-}
-
 __device__ __forceinline__ void signal_add_release(uint32_t *flag) {
   asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
 }
@@ -134,7 +126,7 @@ __device__ __forceinline__ void grid_barrier(const SpParams &p, uint32_t epoch, 
     uint32_t *arrive = p.state[p.rank] + kGridArrive;
     __threadfence();
     atomicAdd(arrive, 1u);
-    if (wait && !wait_counter(arrive, (epoch * 2u + (uint32_t)which) * gridDim.x, true, p.wait_limit)) atomicExch(p.error_flag, code);
+    if (wait && !wait_counter(arrive, (epoch * 3u + (uint32_t)which) * gridDim.x, true, p.wait_limit)) atomicExch(p.error_flag, code);
   }
   __syncthreads();
 }
@@ -343,9 +335,7 @@ __global__ void __launch_bounds__(kThreads, 1) sp_transition_kernel(const SpPara
   const float recip = __frcp_rn(scale);
   if (blockIdx.x == 0 && threadIdx.x == 0) *p.scale_out = scale;
 
-  // ------------------------------------------------------------------ phase 2: quantise; every packed word is stored
-  // straight into every GPU's copy of the prepared activation (multimem.st, 16 / 8 / 4 bytes), so the
-  // transfer overlaps the arithmetic
+  // ------------------------------------------------------------------ phase 2: quantise into this GPU's copy
   const int tasks_per_row = (groups_padded + 31) >> 5;
   for (int c = chunks - 1; c >= 0; --c) {
     const bool cached = c == chunks - 1;
@@ -391,15 +381,15 @@ __global__ void __launch_bounds__(kThreads, 1) sp_transition_kernel(const SpPara
           }
         }
         scale_quantize_group<1, false>(xw, scale, recip, tbl, o);
-        st_multicast_16(p.q_res + (size_t)row * (k / 2) + (size_t)group * 16 + p.mc_delta,
-                        make_uint4(o.q_res[0], o.q_res[1], o.q_res[2], o.q_res[3]));
-        st_multicast_8(p.a_comp + (size_t)row * (k / 4) + (size_t)group * 8 + p.mc_delta, o.a_comp[0], o.a_comp[1]);
+        *reinterpret_cast<uint4 *>(p.q_res + (size_t)row * (k / 2) + (size_t)group * 16) =
+            make_uint4(o.q_res[0], o.q_res[1], o.q_res[2], o.q_res[3]);
+        *reinterpret_cast<uint2 *>(p.a_comp + (size_t)row * (k / 4) + (size_t)group * 8) = make_uint2(o.a_comp[0], o.a_comp[1]);
       }
       const uint32_t mine = o.meta & 0xFFFFu;
       const uint32_t other = __shfl_down_sync(0xffffffffu, mine, 1);
       if ((lane & 1) == 0 && group < groups_padded)
-        st_multicast_4(p.e + (size_t)(group >> 3) * aligned_m * 16 + (size_t)row * 16 + (size_t)(group & 7) * 2 + p.mc_delta,
-                       mine | (other << 16));
+        *reinterpret_cast<uint32_t *>(p.e + (size_t)(group >> 3) * aligned_m * 16 + (size_t)row * 16 + (size_t)(group & 7) * 2) =
+            mine | (other << 16);
       const uint32_t sv = o.sf_sparse;
       const uint32_t s1 = __shfl_down_sync(0xffffffffu, sv, 1);
       const uint32_t s2 = __shfl_down_sync(0xffffffffu, sv, 2);
@@ -408,21 +398,55 @@ __global__ void __launch_bounds__(kThreads, 1) sp_transition_kernel(const SpPara
       const uint32_t r2n = __shfl_down_sync(0xffffffffu, r2, 1);
       if (live) {
         if ((lane & 3) == 0)
-          st_multicast_4(p.sfa_sparse + sf_offset(row, group, groups32) + p.mc_delta, sv | (s1 << 8) | (s2 << 16) | (s3 << 24));
-        if ((lane & 1) == 0) st_multicast_4(p.sf_res + sf_offset(row, 2 * group, k / 16) + p.mc_delta, r2 | (r2n << 16));
+          *reinterpret_cast<uint32_t *>(p.sfa_sparse + sf_offset(row, group, groups32)) = sv | (s1 << 8) | (s2 << 16) | (s3 << 24);
+        if ((lane & 1) == 0) *reinterpret_cast<uint32_t *>(p.sf_res + sf_offset(row, 2 * group, k / 16)) = r2 | (r2n << 16);
       }
     }
   }
 
-  // ---- C: this GPU's multicast stores are out (every CTA fences and arrives, CTA 0 alone waits), tell everyone,
-  //      wait for everyone
+  // ------------------------------------------------------------------ phase 3: push this GPU's rows to every GPU.
+  // A separate pass of contiguous 16-byte multicast stores: storing the packed words straight from the
+  // quantise phase (16 / 8 / 4-byte multimem.st as they are produced) was measured slower (82 against
+  // 63 us per call at two GPUs): the switch wants a warp's multicast stores contiguous.
+  grid_barrier(p, epoch, 2, true, 0x304);  // the packed rows are complete in this GPU's copy
+  {
+    // byte ranges of rows [row0, row0 + rows) in units of 16 bytes; rows is a multiple of 128
+    const size_t n_q = (size_t)p.rows * (k / 2) / 16;
+    const size_t n_a = (size_t)p.rows * (k / 4) / 16;
+    const size_t k_tiles = (size_t)(groups_padded >> 3);
+    const size_t n_e = k_tiles * (size_t)p.rows;
+    const size_t n_sfa = (size_t)(p.rows / 128) * (size_t)(groups32 / 4) * 32;
+    const size_t n_sfr = (size_t)(p.rows / 128) * (size_t)(k / 64) * 32;
+    const size_t total = n_q + n_a + n_e + n_sfa + n_sfr;
+    const size_t stride = (size_t)gridDim.x * kThreads;
+    for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += stride) {
+      uint8_t *src;
+      size_t j = i;
+      if (j < n_q) {
+        src = p.q_res + (size_t)p.row0 * (k / 2) + j * 16;
+      } else if ((j -= n_q) < n_a) {
+        src = p.a_comp + (size_t)p.row0 * (k / 4) + j * 16;
+      } else if ((j -= n_a) < n_e) {
+        const size_t kt = j / p.rows, r = j - kt * p.rows;
+        src = p.e + (kt * aligned_m + p.row0 + r) * 16;
+      } else if ((j -= n_e) < n_sfa) {
+        src = p.sfa_sparse + (size_t)(p.row0 / 128) * (size_t)(groups32 / 4) * 512 + j * 16;
+      } else {
+        j -= n_sfa;
+        src = p.sf_res + (size_t)(p.row0 / 128) * (size_t)(k / 64) * 512 + j * 16;
+      }
+      const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(src));
+      st_multicast_16(src + p.mc_delta, v);
+    }
+  }
+  // ---- C: this GPU's stores are out (grid barrier 3, CTA 0 alone waits), tell everyone, wait for everyone
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
     atomicAdd(my_state + kGridArrive, 1u);
   }
   if (blockIdx.x == 0) {
-    if (threadIdx.x == 0 && !wait_counter(my_state + kGridArrive, (epoch * 2u + 2u) * gridDim.x, true, p.wait_limit))
+    if (threadIdx.x == 0 && !wait_counter(my_state + kGridArrive, (epoch * 3u + 3u) * gridDim.x, true, p.wait_limit))
       atomicExch(p.error_flag, 0x305);
     __syncthreads();
     if ((int)threadIdx.x < p.world) {
