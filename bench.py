@@ -241,7 +241,7 @@ def run_ours(args):
             run(timers, "qkv", "gemm", lambda: lw["qkv"].apply_prepared(prep))
             po = run(timers, "o_proj", "prepare", lambda: lw["o_proj"].local.prepare_input(x["o_in"]))
             if sp is not None:
-                run(timers, "o_proj", "gemm", lambda: lw["o_proj"].local.apply_prepared(po, out=sp.partial))
+                run(timers, "o_proj", "gemm", lambda: lw["o_proj"].local.apply_prepared(po, scatter=sp.scatter))
                 prep, resid = run(timers, "gate_up", "prepare", lambda: sp.transition(resid, lw["gamma2"], eps))
             else:
                 o = run(timers, "o_proj", "gemm", lambda: lw["o_proj"].local.apply_prepared(po))
@@ -250,7 +250,7 @@ def run_ours(args):
             run(timers, "gate_up", "gemm", lambda: lw["gate_up"].apply_prepared(prep))
             pd = run(timers, "down", "prepare", lambda: lw["down"].local.prepare_input(x["d_in"]))
             if sp is not None:
-                run(timers, "down", "gemm", lambda: lw["down"].local.apply_prepared(pd, out=sp.partial))
+                run(timers, "down", "gemm", lambda: lw["down"].local.apply_prepared(pd, scatter=sp.scatter))
                 prep, resid = run(timers, "qkv", "prepare", lambda: sp.transition(resid, nxt["gamma1"], eps))
             else:
                 d = run(timers, "down", "gemm", lambda: lw["down"].local.apply_prepared(pd))
@@ -302,7 +302,7 @@ def run_ours(args):
             # transition kernel: (1) the new residual rows equal residual + sum of the partial products,
             # (2) every rank's prepared activation of ALL rows is byte-identical to what one GPU
             # computes (RMSNorm prepare op) for the gathered rows
-            sp.partial.copy_(partial)
+            lin.local.apply_prepared(prep, scatter=sp.scatter)  # the same GEMM, rows dealt to their owners
             prepared, new_rows = sp.transition(devx["h"], layers[0]["gamma1"], eps)
             rows = [torch.empty_like(new_rows) for _ in range(world)]
             dist.all_gather(rows, new_rows)

@@ -267,18 +267,23 @@ int sharq_linear_gemm_grouped(const void *a_comp, const void *e, const void *sfa
 int sharq_moe_combine(void *out_bf16, const void *y_bf16, const int *dest, const int64_t *selected, const void *w_bf16,
                       int tokens, int top_k, int width, void *stream);
 
-/* No counterpart in the reference (it has no tensor parallelism).  The transition between a
- * row-parallel SharQ linear and the next column-parallel one over the GPUs of one NVSwitch
- * domain, in ONE kernel per GPU, with the residual stream sharded by rows (GPU r owns rows
- * [r*M/world, (r+1)*M/world)):
- *   S   = in-switch fp32 sum over all GPUs of this GPU's rows of the partial products, rounded
- *         to bf16 (partial_multicast: multicast address of the [M,K] bf16 partial-sum buffer,
- *         which every GPU's row-parallel GEMM has written before this call on its stream)
+/* No counterpart in the reference (it has no tensor parallelism).  Row-parallel SharQ linear and the
+ * transition to the next column-parallel one over the GPUs of one NVLink domain, with the residual
+ * stream sharded by rows (GPU r owns rows [r*M/world, (r+1)*M/world)), in two launches per GPU:
+ *
+ * sharq_linear_gemm_scatter: sharq_linear_gemm whose epilogue deals the output rows to their owners:
+ *   row q of this GPU's partial product goes, through the peer mapping d_rank_ptrs[o] of owner
+ *   o = q / (M/world), into block `rank` of GPU o's collection buffer [world][M/world, N] bf16 (plain
+ *   peer stores, so the transfer runs while the GEMM computes).  M % (128*world) == 0, N % 8 == 0.
+ *
+ * sharq_tp_reduce_rmsnorm_prepare_allgather (one cooperative kernel): waits until every GPU has delivered,
+ *   S   = sum over the `world` blocks of partial_blocks (this GPU's collection buffer) in fp32 in rank
+ *         order, rounded to bf16 (partial_blocks == NULL: no sum),
  *   X'  = bf16(residual_in + S) for this GPU's rows, written to residual_out [M/world, K]
- *         (partial_multicast == NULL: X' = residual_in; residual_in == NULL: X' = S)
+ *         (partial_blocks == NULL: X' = residual_in; residual_in == NULL: X' = S),
  *   then RMSNorm statistics of X', the tensor scale from the absmax over ALL GPUs' rows, the
  *   4:8 sparse + residual prepare of this GPU's rows, and the packed rows stored into EVERY
- *   GPU's copy of the prepared activation.
+ *   GPU's copy of the prepared activation (multimem.st).
  * On return of the kernel every GPU's (a_comp, e, sfa_sparse, q_res, sf_res, *scale_out) hold
  * exactly what sharq_fused_rmsnorm_sparse_residual_quantize_x produces for the whole [M,K]
  * matrix X' on one GPU.  The five output buffers are this GPU's copy inside ONE symmetric
@@ -289,10 +294,14 @@ int sharq_moe_combine(void *out_bf16, const void *y_bf16, const int *dest, const
  * Requirements: M % (128*world) == 0, K % 128 == 0, K/32 <= 1024, 16-byte aligned buffers, the
  * same sequence of calls on every GPU.  Every cross-GPU wait is bounded (about ten seconds); one
  * that runs out stores a code 0x301..0x306 in *error_flag and the outputs are undefined.  Uses
- * multimem.ld_reduce / multimem.st and peer stores only. */
+ * plain peer stores and multimem.st only. */
+int sharq_linear_gemm_scatter(const void *a_comp, const void *e, const void *sfa_sparse, const void *q_res, const void *sf_res,
+                              const void *qw, const void *sfw_sparse, const void *sfw_dense, int m, int n, int k, float alpha,
+                              const float *alpha_dev, void *const *d_rank_ptrs, int rank, int world, int *error_flag,
+                              void *stream);
 size_t sharq_tp_transition_state_bytes(void);
 size_t sharq_tp_transition_workspace_bytes(int rows);
-int sharq_tp_reduce_rmsnorm_prepare_allgather(const void *partial_multicast, const void *residual_in_bf16,
+int sharq_tp_reduce_rmsnorm_prepare_allgather(const void *partial_blocks, const void *residual_in_bf16,
                                               void *residual_out_bf16, const void *rmsnorm_weight_bf16, float rmsnorm_eps,
                                               int m, int n, int k, void *workspace, size_t workspace_bytes, void *a_comp,
                                               void *e, void *sfa_sparse, void *q_res, void *sf_res,

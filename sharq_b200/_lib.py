@@ -61,6 +61,8 @@ SIGNATURES = {
         c_int, [_P, _P, _P, _P, _P, c_int, POINTER(c_void_p), POINTER(c_void_p), POINTER(c_void_p), _P, _P, c_float, c_int,
                 c_int, c_int, _P, _P, _P]),
     "sharq_moe_combine": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, _P]),
+    "sharq_linear_gemm_scatter": (
+        c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_float, _P, POINTER(c_void_p), c_int, c_int, _P, _P]),
     "sharq_tp_transition_state_bytes": (c_size_t, []),
     "sharq_tp_transition_workspace_bytes": (c_size_t, [c_int]),
     "sharq_tp_reduce_rmsnorm_prepare_allgather": (

@@ -337,11 +337,47 @@ int sharq_moe_combine(void *out_bf16, const void *y_bf16, const int *dest, const
                     "moe_combine");
 }
 
+int sharq_linear_gemm_scatter(const void *a_comp, const void *e, const void *sfa_sparse, const void *q_res, const void *sf_res,
+                              const void *qw, const void *sfw_sparse, const void *sfw_dense, int m, int n, int k, float alpha,
+                              const float *alpha_dev, void *const *d_rank_ptrs, int rank, int world, int *error_flag,
+                              void *stream) {
+  SHARQ_REQUIRE(world >= 2 && world <= sharq::kGemmMaxPeers, "world must be in [2, %d]", sharq::kGemmMaxPeers);
+  SHARQ_REQUIRE(rank >= 0 && rank < world, "rank must be in [0, world)");
+  SHARQ_REQUIRE(m > 0 && n > 0 && k > 0 && m % (128 * world) == 0 && n % 8 == 0 && k % 128 == 0,
+                "needs M %% (128 * world) == 0, N %% 8 == 0, K %% 128 == 0");
+  SHARQ_REQUIRE(a_comp && e && sfa_sparse && q_res && sf_res && qw && sfw_sparse && sfw_dense && d_rank_ptrs && error_flag,
+                "null buffer");
+  sharq::GemmArgs g;
+  g.a_comp = a_comp;
+  g.e = e;
+  g.sfa_sparse = sfa_sparse;
+  g.a_dense = q_res;
+  g.sfa_dense = sf_res;
+  g.b = qw;
+  g.sfb_sparse = sfw_sparse;
+  g.sfb_dense = sfw_dense;
+  g.alpha = alpha;
+  g.alpha_ptr = alpha_dev;
+  g.m = m;
+  g.n = n;
+  g.k = k;
+  g.tile_n = g_tile_n;
+  g.error_flag = error_flag;
+  g.scatter_world = world;
+  g.scatter_rank = rank;
+  for (int r = 0; r < world; ++r) {
+    SHARQ_REQUIRE(d_rank_ptrs[r] != nullptr && (reinterpret_cast<uintptr_t>(d_rank_ptrs[r]) & 15) == 0,
+                  "d_rank_ptrs[%d] must be a 16-byte aligned pointer", r);
+    g.d_peer[r] = d_rank_ptrs[r];
+  }
+  return check_cuda(sharq::run_gemm(g, as_stream(stream)), "linear_gemm_scatter");
+}
+
 size_t sharq_tp_transition_state_bytes(void) { return sharq::sp_transition_state_bytes(); }
 
 size_t sharq_tp_transition_workspace_bytes(int rows) { return rows > 0 ? sharq::sp_transition_workspace_bytes(rows) : 0; }
 
-int sharq_tp_reduce_rmsnorm_prepare_allgather(const void *partial_multicast, const void *residual_in, void *residual_out,
+int sharq_tp_reduce_rmsnorm_prepare_allgather(const void *partial_blocks, const void *residual_in, void *residual_out,
                                               const void *rmsnorm_weight, float eps, int m, int n, int k, void *workspace,
                                               size_t workspace_bytes, void *a_comp, void *e, void *sfa_sparse, void *q_res,
                                               void *sf_res, long long multicast_delta, float *scale_out,
@@ -354,13 +390,13 @@ int sharq_tp_reduce_rmsnorm_prepare_allgather(const void *partial_multicast, con
                 "M must be a positive multiple of 128 * world (every GPU owns whole 128-row bands), got M = %d, world = %d", m,
                 world);
   SHARQ_REQUIRE(k % 128 == 0 && k / 32 <= 1024, "K must be a multiple of 128 with K/32 <= 1024, got %d", k);
-  SHARQ_REQUIRE(partial_multicast || residual_in, "partial sums or a residual (or both) must be given");
+  SHARQ_REQUIRE(partial_blocks || residual_in, "partial products or a residual (or both) must be given");
   SHARQ_REQUIRE(residual_out && rmsnorm_weight && a_comp && e && sfa_sparse && q_res && sf_res && scale_out && rank_state_ptrs &&
                     error_flag,
                 "null buffer");
   SHARQ_REQUIRE(workspace && workspace_bytes >= sharq::sp_transition_workspace_bytes(m / world),
                 "workspace too small: need %zu bytes", sharq::sp_transition_workspace_bytes(m / world));
-  const void *aligned[] = {partial_multicast, residual_in, residual_out, rmsnorm_weight, a_comp, e, sfa_sparse, q_res, sf_res};
+  const void *aligned[] = {partial_blocks, residual_in, residual_out, rmsnorm_weight, a_comp, e, sfa_sparse, q_res, sf_res};
   for (const void *ptr : aligned)
     SHARQ_REQUIRE((reinterpret_cast<uintptr_t>(ptr) & 15) == 0, "buffers must be 16-byte aligned");
   SHARQ_REQUIRE((multicast_delta & 15) == 0, "multicast_delta must be a multiple of 16");
@@ -368,7 +404,7 @@ int sharq_tp_reduce_rmsnorm_prepare_allgather(const void *partial_multicast, con
     SHARQ_REQUIRE(rank_state_ptrs[i] != nullptr && (reinterpret_cast<uintptr_t>(rank_state_ptrs[i]) & 15) == 0,
                   "rank_state_ptrs[%d] must be a 16-byte aligned pointer", i);
   sharq::SpTransitionArgs a;
-  a.partial_multicast = partial_multicast;
+  a.partial_blocks = partial_blocks;
   a.residual_in = residual_in;
   a.residual_out = residual_out;
   a.gamma = rmsnorm_weight;

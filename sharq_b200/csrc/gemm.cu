@@ -107,6 +107,12 @@ struct GemmParams {
   int k_splits;
   float *splitk_acc;
   int staged_store;  // output tiles are transposed through shared memory for coalesced stores (N % 8 == 0)
+  // Scatter mode (row-parallel linear under tensor parallelism): the output rows are dealt to their owner GPUs.
+  // Row r belongs to GPU o = r / scatter_rows and is stored, through the peer mapping, into d_peer[o] at row
+  // scatter_rank * scatter_rows + (r - o * scatter_rows): every GPU collects one [scatter_rows, n] block per
+  // source GPU.  scatter_rows is a multiple of 128, so a tile has one owner.  scatter_rows == 0: plain output.
+  __nv_bfloat16 *d_peer[kGemmMaxPeers];
+  int scatter_rows, scatter_rank;
 };
 
 // Grouped launch (mixture-of-experts layers): the rows of the activation are sorted by group
@@ -523,6 +529,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap &tm_w, const CUtenso
       }
       if (stage != nullptr) {
         const int row0 = m_tile * kBM + quad * 32;
+        __nv_bfloat16 *d_base = p.d;
+        if (p.scatter_rows > 0) {
+          const int owner = (m_tile * kBM) / p.scatter_rows;
+          d_base = p.d_peer[owner] + ((long long)p.scatter_rank - owner) * p.scatter_rows * (long long)p.n;
+        }
 #pragma unroll
         for (int c = 0; c < kColsPerEpiWarp / 32; ++c) {
           const int col0 = col_base + 32 * c;
@@ -534,7 +545,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap &tm_w, const CUtenso
             const int r = it * 8 + (lane >> 2);
             const uint4 v = *reinterpret_cast<const uint4 *>(stage + r * 64 + (((lane & 3) ^ ((r >> 1) & 3)) << 4));
             if (row0 + r < p.m && gcol < p.n)
-              *reinterpret_cast<uint4 *>(p.d + (size_t)(row0 + r) * p.n + gcol) = v;
+              *reinterpret_cast<uint4 *>(d_base + (size_t)(row0 + r) * p.n + gcol) = v;
           }
           __syncwarp();
         }
@@ -677,7 +688,7 @@ cudaError_t launch(const GemmArgs &a, cudaStream_t stream) {
   if (SPARSE && !make_tmap_bytes(&tm_ac, a.a_comp, (uint64_t)a.m, (uint64_t)a.k / 4, kBM, 64, CU_TENSOR_MAP_SWIZZLE_64B))
     return cudaErrorInvalidValue;
   GemmParams p{};
-  p.staged_store = (a.n % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.d) & 15) == 0);
+  p.staged_store = (a.n % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.scatter_world > 1 ? a.d_peer[0] : a.d) & 15) == 0);
   p.e = static_cast<const uint8_t *>(a.e);
   p.sfa_sparse = static_cast<const uint8_t *>(a.sfa_sparse);
   p.sfa_dense = static_cast<const uint8_t *>(a.sfa_dense);
@@ -693,6 +704,18 @@ cudaError_t launch(const GemmArgs &a, cudaStream_t stream) {
   p.n = a.n;
   p.k = a.k;
   p.error_flag = a.error_flag;
+  p.scatter_rows = 0;
+  if (a.scatter_world > 1) {
+    // dealing rows to their owners needs whole 128-row tiles per owner and the coalesced store path
+    if (a.scatter_world > kGemmMaxPeers || a.m % (128 * a.scatter_world) != 0 || !p.staged_store || a.c_in != nullptr)
+      return cudaErrorInvalidValue;
+    for (int r = 0; r < a.scatter_world; ++r) {
+      if (a.d_peer[r] == nullptr || (reinterpret_cast<uintptr_t>(a.d_peer[r]) & 15) != 0) return cudaErrorInvalidValue;
+      p.d_peer[r] = static_cast<__nv_bfloat16 *>(a.d_peer[r]);
+    }
+    p.scatter_rows = a.m / a.scatter_world;
+    p.scatter_rank = a.scatter_rank;
+  }
   const int n_tiles = (a.n + BN - 1) / BN;
   const int m_units = PAIR ? (a.m + 255) / 256 : (a.m + kBM - 1) / kBM;
   int units = m_units * n_tiles;
@@ -701,7 +724,8 @@ cudaError_t launch(const GemmArgs &a, cudaStream_t stream) {
   p.k_splits = 1;
   p.splitk_acc = nullptr;
   const int k_stages = (a.k + kBK - 1) / kBK;
-  if (!PAIR && m_units == 1 && a.workspace != nullptr && a.workspace_bytes >= (size_t)a.m * a.n * sizeof(float)) {
+  if (!PAIR && m_units == 1 && a.scatter_world <= 1 && a.workspace != nullptr &&
+      a.workspace_bytes >= (size_t)a.m * a.n * sizeof(float)) {
     int splits = sms / units;
     if (splits > k_stages / 2) splits = k_stages / 2;  // at least two K stages per unit
     // the fp32 reductions cost M x N x splits atomics: measured worth it for M <= 64 (qkv

@@ -6,6 +6,8 @@
 
 namespace sharq {
 
+constexpr int kGemmMaxPeers = 16;
+
 struct GemmArgs {
   // Sparse main path operand (all three null => dense-only GEMM).
   const void *a_comp = nullptr;      // [m, k/4] compressed e2m1 pairs
@@ -32,6 +34,11 @@ struct GemmArgs {
   // (fp32 partial sums are accumulated there, a second kernel applies the epilogue).
   void *workspace = nullptr;
   size_t workspace_bytes = 0;
+  // Scatter mode (scatter_world > 1, `d` unused): the m / scatter_world rows owned by GPU o are stored into
+  // d_peer[o] (GPU o's collection buffer as mapped on this GPU, [scatter_world][m / scatter_world][n] bf16) at
+  // block scatter_rank.  Needs m % (128 * scatter_world) == 0 and n % 8 == 0.
+  void *d_peer[kGemmMaxPeers] = {};
+  int scatter_world = 0, scatter_rank = 0;
 };
 
 cudaError_t run_gemm(const GemmArgs &args, cudaStream_t stream);

@@ -19,8 +19,9 @@
 //
 // Synchronisation (state words in symmetric memory, zero-initialised once; everything
 // resets itself, so a captured launch can be replayed):
-//   A  "partial sums complete": every GPU signals all others when its kernel starts (its GEMM
-//      precedes it on the stream); all CTAs wait for all GPUs before the first reduce.
+//   A  "partial products delivered": every GPU signals all others when its kernel starts (its GEMM,
+//      whose epilogue stored into the peers, precedes it on the stream); all CTAs wait for all GPUs
+//      before the first read of the collection buffer.
 //   B  tensor absmax: after a grid-wide barrier CTA 0 stores {absmax, launch number} as one
 //      8-byte word into every GPU's state; all CTAs wait until all words carry the number.
 //   C  "broadcast landed": after its packed rows are stored to all GPUs, a GPU signals all
@@ -58,7 +59,8 @@ constexpr int kAmaxLocal = 66;   // [2] this GPU's absmax accumulator, by launch
 constexpr int kStateWords = 80;
 
 struct SpParams {
-  const uint8_t *partial_mc;          // multicast address of the partial sums [m, k] bf16, or null
+  const uint8_t *partial;             // this GPU's collection buffer [world][rows, k] bf16 (block s: GPU s's partial
+                                      // products of this GPU's rows, stored there by GPU s's GEMM), or null
   const __nv_bfloat16 *residual_in;   // this GPU's rows [rows, k], or null
   __nv_bfloat16 *residual_out;        // this GPU's rows of the new residual stream [rows, k]
   const __nv_bfloat16 *gamma;
@@ -75,13 +77,6 @@ struct SpParams {
   long long wait_limit;               // clock cycles a wait may take
   int *error_flag;
 };
-
-__device__ __forceinline__ void ld_reduce_bf16x8(const uint8_t *mc_addr, uint4 &v) {
-  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(mc_addr)
-               : "memory");
-}
 
 __device__ __forceinline__ void st_multicast_16(uint8_t *mc_addr, const uint4 &v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y),
@@ -196,46 +191,54 @@ __global__ void __launch_bounds__(kThreads, 1) sp_transition_kernel(const SpPara
   for (int c = 0; c < chunks; ++c) {
     const int c_rows = chunk_size(c), c_row0 = row_begin + chunk_first_row(c);
     if (c > 0) __syncthreads();
-    // 1a: reduce + add, 16 bytes per lane with neighbouring lanes on neighbouring addresses (the
-    // switch serves multimem requests best when a warp's request is contiguous); the new
-    // residual rows go to global memory and, group-permuted, into the shared-memory cache
+    // 1a: sum of the `world` partial blocks (fp32, in rank order, one rounding to bf16 - the arithmetic of the
+    // peer-copy all-reduce kernel) + residual add; the new residual rows go to global memory and,
+    // group-permuted, into the shared-memory cache.  The blocks were written by other GPUs: L2 loads (.cg).
     const int n_vecs = c_rows * row_vecs;
-    constexpr int kInFlight = 4;
-    for (int v0 = threadIdx.x; v0 < n_vecs; v0 += kInFlight * kThreads) {
-      uint4 sv[kInFlight], rv[kInFlight];
+    const size_t block_vecs = (size_t)p.rows * row_vecs;  // 16-byte vectors per source block
+    for (int v0 = threadIdx.x; v0 < n_vecs; v0 += 2 * kThreads) {
 #pragma unroll
-      for (int u = 0; u < kInFlight; ++u) {
-        const int v = v0 + u * kThreads;
-        sv[u] = make_uint4(0u, 0u, 0u, 0u);
-        rv[u] = make_uint4(0u, 0u, 0u, 0u);
-        if (v < n_vecs) {
-          const int rl = v / row_vecs, i = v - rl * row_vecs;
-          const size_t off_l = ((size_t)(c_row0 + rl) * row_vecs + i) * 16;           // bytes, local row block
-          const size_t off_g = ((size_t)(p.row0 + c_row0 + rl) * row_vecs + i) * 16;  // bytes, whole activation
-          if (p.partial_mc != nullptr) ld_reduce_bf16x8(p.partial_mc + off_g, sv[u]);
-          if (p.residual_in != nullptr)
-            rv[u] = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const uint8_t *>(p.residual_in) + off_l));
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < kInFlight; ++u) {
+      for (int u = 0; u < 2; ++u) {
         const int v = v0 + u * kThreads;
         if (v >= n_vecs) continue;
         const int rl = v / row_vecs, i = v - rl * row_vecs;
-        const uint32_t s4[4] = {sv[u].x, sv[u].y, sv[u].z, sv[u].w};
-        const uint32_t r4[4] = {rv[u].x, rv[u].y, rv[u].z, rv[u].w};
+        const size_t vec_l = (size_t)(c_row0 + rl) * row_vecs + i;  // vector index inside this GPU's row block
         uint32_t w[4];
+        uint4 rv = make_uint4(0u, 0u, 0u, 0u);
+        if (p.residual_in != nullptr) rv = __ldg(reinterpret_cast<const uint4 *>(p.residual_in) + vec_l);
+        if (p.partial != nullptr) {
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          const uint4 *blk = reinterpret_cast<const uint4 *>(p.partial) + vec_l;
+          for (int r0 = 0; r0 < p.world; r0 += 4) {  // four source blocks in flight
+            uint4 pv[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+              if (r0 + t < p.world) pv[t] = __ldcg(blk + (size_t)(r0 + t) * block_vecs);
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              if (r0 + t < p.world) {
+                const uint32_t pw[4] = {pv[t].x, pv[t].y, pv[t].z, pv[t].w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  acc[2 * q] += lo_f(pw[q]);
+                  acc[2 * q + 1] += hi_f(pw[q]);
+                }
+              }
+            }
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) w[q] = pack_bf16x2(acc[2 * q], acc[2 * q + 1]);
+        }
+        const uint32_t r4[4] = {rv.x, rv.y, rv.z, rv.w};
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          if (p.partial_mc == nullptr)
+          if (p.partial == nullptr)
             w[q] = r4[q];
-          else if (p.residual_in == nullptr)
-            w[q] = s4[q];
-          else  // bf16(residual + sum), rounded like the ATen add of two bf16 tensors
-            w[q] = pack_bf16x2(__fadd_rn(lo_f(r4[q]), lo_f(s4[q])), __fadd_rn(hi_f(r4[q]), hi_f(s4[q])));
+          else if (p.residual_in != nullptr)  // bf16(residual + sum), rounded like the ATen add of two bf16 tensors
+            w[q] = pack_bf16x2(__fadd_rn(lo_f(r4[q]), lo_f(w[q])), __fadd_rn(hi_f(r4[q]), hi_f(w[q])));
         }
         const uint4 out = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.residual_out) + ((size_t)(c_row0 + rl) * row_vecs + i) * 16) = out;
+        *(reinterpret_cast<uint4 *>(p.residual_out) + vec_l) = out;
         cache[(size_t)rl * row_vecs + cache_slot(i >> 2, i & 3)] = out;
       }
     }
@@ -482,7 +485,7 @@ cudaError_t run_sp_transition(const SpTransitionArgs &a, cudaStream_t stream) {
   }
   const int sms = sms_of[dev];
   SpParams p{};
-  p.partial_mc = static_cast<const uint8_t *>(a.partial_multicast);
+  p.partial = static_cast<const uint8_t *>(a.partial_blocks);
   p.residual_in = static_cast<const __nv_bfloat16 *>(a.residual_in);
   p.residual_out = static_cast<__nv_bfloat16 *>(a.residual_out);
   p.gamma = static_cast<const __nv_bfloat16 *>(a.gamma);

@@ -9,7 +9,7 @@ namespace sharq {
 constexpr int kSpMaxRanks = 16;
 
 struct SpTransitionArgs {
-  const void *partial_multicast = nullptr;  // multicast address of the partial sums [m, k] bf16 (null: none)
+  const void *partial_blocks = nullptr;     // this GPU's collection buffer [world][m / world, k] bf16 (null: none)
   const void *residual_in = nullptr;        // this GPU's rows of the residual stream [m / world, k] bf16 (null: none)
   void *residual_out = nullptr;             // this GPU's rows of the new residual stream
   const void *gamma = nullptr;              // RMSNorm weight [k] bf16

@@ -240,18 +240,18 @@ class SharqDecoderLayer(torch.nn.Module):
         """One layer with the residual stream sharded by rows over the ranks (tp.SequenceParallelContext).
         prepared: the RMSNorm-prepared input of qkv for ALL b*s rows (from the previous transition);
         x_local: this rank's rows of the residual stream.  The two transitions (after o_proj with this
-        layer's post-attention norm, after down_proj with the NEXT layer's input norm) each run as one
-        kernel: reduce-scatter of the partial products, residual add, RMSNorm prepare of the local
-        rows, all-gather of the packed activation.  -> (prepared input of the next layer's qkv, x_local)."""
+        layer's post-attention norm, after down_proj with the NEXT layer's input norm): the row-parallel GEMM
+        deals its output rows to their owner ranks from its epilogue, and one kernel sums them, adds the
+        residual, prepares the local rows (RMSNorm fused) and all-gathers the packed activation.  -> (prepared input of the next layer's qkv, x_local)."""
         cfg = self.cfg
         qkv = self.qkv.apply_prepared(prepared)
         q, k, v = _split_heads(qkv, b, s, self.local_heads, self.local_kv, cfg.head_dim, cos, sin, True)
         attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
         attn2 = attn.transpose(1, 2).reshape(b * s, self.local_heads * cfg.head_dim)
-        self.o_proj.local.apply_prepared(self.o_proj.local.prepare_input(attn2), out=sp.partial)
+        self.o_proj.local.apply_prepared(self.o_proj.local.prepare_input(attn2), scatter=sp.scatter)
         prepared, x_local = sp.transition(x_local, self.post_norm, cfg.eps)
         gu = self.gate_up.apply_prepared(prepared)
-        self.down.local.apply_prepared(self.down.local.prepare_input_swiglu(gu), out=sp.partial)
+        self.down.local.apply_prepared(self.down.local.prepare_input_swiglu(gu), scatter=sp.scatter)
         return sp.transition(x_local, next_gamma, cfg.eps)
 
     @torch.no_grad()

@@ -499,10 +499,13 @@ def sparse_matmul_tensor_scale(A_comp, B, E, SFA, SFB, M: int, N: int, K: int, a
 
 def sharq_linear_gemm(A_comp, E, SFA_sparse, Q_res, SF_res, QW, SFW_sparse, SFW_dense, alpha,
                       bias: Optional[torch.Tensor] = None, alpha_host: float = 1.0,
-                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      out: Optional[torch.Tensor] = None, scatter=None) -> Optional[torch.Tensor]:
     """Fused sparse-main + dense-residual GEMM on a prepared activation (one launch).
     alpha: python float or 1-element CUDA float32 tensor; the factor applied is
-    alpha * alpha_host.  out: optional contiguous bf16 [M, N] tensor to write into."""
+    alpha * alpha_host.  out: optional contiguous bf16 [M, N] tensor to write into.
+    scatter=(rank_ptrs, rank, world): row-parallel output under tensor parallelism; the rows are dealt to the
+    collection buffers of their owner GPUs (rank_ptrs: ctypes array of their mappings, see
+    sharq_linear_gemm_scatter); nothing is returned."""
     M, K = int(Q_res.shape[0]), int(Q_res.shape[1]) * 2
     N = int(QW.shape[0])
     dev = Q_res.device
@@ -516,13 +519,23 @@ def sharq_linear_gemm(A_comp, E, SFA_sparse, Q_res, SF_res, QW, SFW_sparse, SFW_
     if bias is not None:
         _check(bias.is_cuda and bias.dtype == torch.bfloat16 and bias.numel() == N and bias.is_contiguous(),
                "bias must be a contiguous CUDA bfloat16 tensor with N elements")
+    alpha_t = alpha if isinstance(alpha, torch.Tensor) else None
+    if scatter is not None:
+        _check(bias is None and out is None, "scatter mode takes neither bias nor out")
+        rank_ptrs, rank, world = scatter
+        with _on_device(dev):
+            _lib.check(_lib.lib().sharq_linear_gemm_scatter(
+                _ptr(A_comp), _ptr(E), _ptr(SFA_sparse), _ptr(Q_res), _ptr(SF_res), _ptr(QW), _ptr(SFW_sparse),
+                _ptr(SFW_dense), M, N, K, float(alpha_host) if alpha_t is not None else float(alpha) * float(alpha_host),
+                None if alpha_t is None else _scale_ptr(alpha_t, Q_res, "alpha"), rank_ptrs, int(rank), int(world),
+                _ptr(_error_flag(dev)), _stream(dev)))
+        return None
     if out is None:
         D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
     else:
         _check(out.is_cuda and out.device == dev and out.dtype == torch.bfloat16 and out.is_contiguous()
                and tuple(out.shape) == (M, N), "out must be a contiguous CUDA bfloat16 tensor shaped [M, N]")
         D = out
-    alpha_t = alpha if isinstance(alpha, torch.Tensor) else None
     ws, ws_bytes = _gemm_scratch(M, N, dev)
     with _on_device(dev):
         _lib.check(_lib.lib().sharq_linear_gemm_ws(

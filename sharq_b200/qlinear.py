@@ -137,10 +137,18 @@ class QLinearLayer(nn.Module):
         return ("SHARQ", a_comp, e, sfa, q_res, sf_res, scale_x)
 
     @torch.no_grad()
-    def apply_prepared(self, prepared, out=None):
+    def apply_prepared(self, prepared, out=None, scatter=None):
         """out: optional bf16 [M, N] tensor the fused SharQ GEMM writes into (used by the
-        tensor-parallel layers to place partial sums in symmetric memory)."""
+        tensor-parallel layers to place partial sums in symmetric memory).  scatter: see
+        ops.sharq_linear_gemm (row-parallel output dealt to the owner GPUs; returns None)."""
         tag = prepared[0]
+        if scatter is not None:
+            if not (tag == "SHARQ" and self.fused_gemm and self.bias is None):
+                raise ValueError("scatter= needs the fused SharQ GEMM of a layer without bias")
+            _, a_comp, e, sfa, q_res, sf_res, scale_x = prepared
+            return ops.sharq_linear_gemm(a_comp, e, sfa, q_res, sf_res, self.weight_q, self.scale_w_sparse,
+                                         self.scale_w_dense, scale_x.reshape(1), alpha_host=self.weight_scale_host,
+                                         scatter=scatter)
         if out is not None and not ((tag == "SHARQ" and self.fused_gemm) or (tag == "NVFP4" and self.bias is None)):
             raise ValueError("out= is only supported by the fused SharQ GEMM and the bias-free dense NVFP4 GEMM")
         if tag == "SHARQ":

@@ -118,7 +118,8 @@ class SymmetricSumBuffer:
         self.flag_ptrs = (ctypes.c_void_p * self.world)(*[b + flags_at for b in bases])
         self.bases = bases
         # two ranks: plain peer loads/stores move fewer bytes per link than the multicast object
-        self.peer_copy = self.world == 2 and os.environ.get("SHARQ_TP_ALLREDUCE", "auto").lower() != "multimem"
+        mode = os.environ.get("SHARQ_TP_ALLREDUCE", "auto").lower()
+        self.peer_copy = (mode == "peer" and self.world <= 4) or (self.world == 2 and mode != "multimem")
         self.handle = handle
         self._next = 0
 
@@ -155,8 +156,8 @@ _SUM_BUFFERS = {}
 
 def _multimem_wanted(group) -> bool:
     mode = os.environ.get("SHARQ_TP_ALLREDUCE", "auto").lower()
-    if mode not in ("auto", "multimem", "nccl"):
-        raise ValueError("SHARQ_TP_ALLREDUCE must be auto, multimem or nccl")
+    if mode not in ("auto", "multimem", "peer", "nccl"):
+        raise ValueError("SHARQ_TP_ALLREDUCE must be auto, multimem, peer or nccl")
     if mode == "nccl":
         return False
     usable = torch.cuda.is_available() and dist.get_backend(group) == "nccl"
@@ -212,8 +213,9 @@ class SequenceParallelContext:
     """Symmetric-memory buffers and state of the one-kernel layer transition
     (csrc/sp_transition.cu) for activations of a fixed shape [m, hidden]:
 
-    * `partial` - the [m, hidden] bf16 buffer the row-parallel GEMM (o_proj, down_proj) writes its
-      partial products into (pass `partial` as `out=` of the GEMM);
+    * the collection buffer [world][m / world, hidden] bf16: block s receives, from rank s's row-parallel
+      GEMM (o_proj, down_proj; pass `scatter` as `scatter=` of `QLinearLayer.apply_prepared`), rank s's
+      partial products of THIS rank's rows, while that GEMM computes;
     * the prepared activation of all m rows (A_comp, E, both scale buffers, Q_res), which
       `transition` fills on every rank;
     * the state words of the cross-rank hand-shakes.
@@ -264,8 +266,10 @@ class SequenceParallelContext:
         dist.barrier(group)
         state_at = self._off["state"][0]
         self.state_ptrs = (ctypes.c_void_p * self.world)(*[b + state_at for b in bases])
-        self.partial = self._view("partial").view(torch.bfloat16).view(m, hidden)
-        self.partial_multicast = self.storage.data_ptr() + self._off["partial"][0] + self.multicast_delta
+        partial_at = self._off["partial"][0]
+        self.blocks = self._view("partial").view(torch.bfloat16).view(self.world, self.rows, hidden)  # block s: from rank s
+        self.partial_ptrs = (ctypes.c_void_p * self.world)(*[b + partial_at for b in bases])
+        self.scatter = (self.partial_ptrs, self.rank, self.world)  # `scatter=` argument of the row-parallel GEMM
         self.scale = torch.zeros((), dtype=torch.float32, device=device)
         self.workspace = torch.empty(int(lib.sharq_tp_transition_workspace_bytes(self.rows)), dtype=torch.uint8, device=device)
 
@@ -276,13 +280,22 @@ class SequenceParallelContext:
     def row_bounds(self) -> Tuple[int, int]:
         return self.rank * self.rows, (self.rank + 1) * self.rows
 
+    def deliver(self, partial: torch.Tensor) -> None:
+        """Deal the rows of a full [m, hidden] bf16 partial product to their owners' collection buffers, as the
+        scatter-mode GEMM epilogue does (peer copies; for tests and checks that have the partial product as a tensor).
+        Collective in effect: every rank must call it, and a barrier must follow before `transition`."""
+        for owner in range(self.world):
+            dst = self.handle.get_buffer(owner, (self.world, self.rows, self.hidden), torch.bfloat16,
+                                         self._off["partial"][0] // 2)
+            dst[self.rank].copy_(partial[owner * self.rows:(owner + 1) * self.rows])
+
     def transition(self, residual_local: Optional[torch.Tensor], gamma: torch.Tensor, eps: float, use_partial: bool = True,
                    out_features_hint: int = 0):
         """-> (prepared, new_residual_local).  prepared is the reference's ("SHARQ", A_comp, E, SFA_sparse,
         Q_res, SF_res, scale) tuple for ALL m rows (views of this rank's symmetric buffers, valid until
-        the next transition); new_residual_local = bf16(residual_local + sum over ranks of `partial`)
-        for this rank's rows.  The row-parallel GEMM that wrote `partial` must precede this call on
-        the current stream of every rank."""
+        the next transition); new_residual_local = bf16(residual_local + sum over ranks of the partial
+        products) for this rank's rows.  The row-parallel GEMM in scatter mode must precede this call
+        on the current stream of every rank."""
         from . import _lib, ops
 
         if residual_local is None and not use_partial:
@@ -296,7 +309,7 @@ class SequenceParallelContext:
         a_comp, e, sfa, q_res, sf_res = (self._view(n) for n in ("a_comp", "e", "sfa", "q_res", "sf_res"))
         with torch.cuda.device(self.device):
             _lib.check(_lib.lib().sharq_tp_reduce_rmsnorm_prepare_allgather(
-                ctypes.c_void_p(self.partial_multicast) if use_partial else None,
+                ctypes.c_void_p(self.blocks.data_ptr()) if use_partial else None,
                 None if residual_local is None else ctypes.c_void_p(residual_local.data_ptr()),
                 ctypes.c_void_p(new_residual.data_ptr()), ctypes.c_void_p(gamma.data_ptr()), float(eps), self.m,
                 int(out_features_hint), self.hidden, ctypes.c_void_p(self.workspace.data_ptr()), self.workspace.numel(),

@@ -24,7 +24,7 @@ def check_case(ctx, m, hidden, rank, world, dev, seed, use_partial, use_residual
     part = (0.3 * H.config0_x(m, hidden, seed + 10 + rank).float()).to(torch.bfloat16).to(dev)  # differs per rank
     b, e = ctx.row_bounds()
     if use_partial:
-        ctx.partial.copy_(part)
+        ctx.deliver(part)
     res_local = full_res[b:e].contiguous() if use_residual else None
     torch.cuda.synchronize()
     dist.barrier()
@@ -35,17 +35,17 @@ def check_case(ctx, m, hidden, rank, world, dev, seed, use_partial, use_residual
     rows = [torch.empty_like(new_res) for _ in range(world)]
     dist.all_gather(rows, new_res)
     full_new = torch.cat(rows).contiguous()
-    # expected new residual: bf16(residual + bf16(fp32 sum of the partial products))
+    # expected new residual: bf16(residual + bf16(fp32 sum of the partial products in rank order)), exactly
     if use_partial:
         parts = [torch.empty_like(part) for _ in range(world)]
         dist.all_gather(parts, part)
-        s32 = torch.stack(parts).float().sum(0)
+        s32 = parts[0].float()
+        for other in parts[1:]:
+            s32 = s32 + other.float()
         want = (full_res.float() + s32.to(torch.bfloat16).float()).to(torch.bfloat16) if use_residual else s32.to(torch.bfloat16)
-        err = (full_new.float() - want.float()).abs()
-        tol = want.float().abs() * 2.0 ** -7 + s32.abs() * 2.0 ** -7 + 1e-30  # one bf16 ulp of the sum or of the result
-        if not bool((err <= tol).all()):
+        if not torch.equal(full_new, want):
             ok = False
-            say(f"new residual differs from residual + sum: max err {float(err.max())}")
+            say(f"new residual differs from residual + sum: max err {float((full_new.float() - want.float()).abs().max())}")
     elif not torch.equal(full_new, full_res):
         ok = False
         say("new residual differs from the residual although there were no partial sums")
@@ -83,13 +83,35 @@ def main():
                 raise RuntimeError("no sequence-parallel context (NVLink multicast missing?)")
             for rep, (use_partial, use_residual) in enumerate(((True, True), (True, True), (False, True), (True, False))):
                 ok = check_case(ctx, m, hidden, rank, world, dev, 7 * rep + m % 13, use_partial, use_residual, say) and ok
+        # the scatter-mode GEMM deals its output rows to their owners: block s of this rank's collection buffer
+        # must hold rank s's plain GEMM output for this rank's rows
+        from tests import helpers as H2
+
+        ctx = tp.sequence_parallel_context(2048, 4096, None, dev)
+        lin = tp.RowParallelSharqLinear(H2.config0_w(4096, 1024 * world, 3).to(dev))
+        kb, ke = tp.shard_bounds(1024 * world, world, rank, tp.K_ALIGN)
+        prep = lin.local.prepare_input(H2.config0_x(2048, 1024 * world, 5)[:, kb:ke].contiguous().to(dev))
+        plain = lin.local.apply_prepared(prep)
+        torch.cuda.synchronize()
+        dist.barrier()
+        lin.local.apply_prepared(prep, scatter=ctx.scatter)
+        torch.cuda.synchronize()
+        ops.check_device_errors()
+        dist.barrier()
+        outs = [torch.empty_like(plain) for _ in range(world)]
+        dist.all_gather(outs, plain)
+        b0, e0 = ctx.row_bounds()
+        for src in range(world):
+            if not torch.equal(ctx.blocks[src], outs[src][b0:e0]):
+                ok = False
+                say(f"scatter GEMM: block {src} differs from rank {src}'s output rows")
         # replay from a CUDA graph: the state words reset themselves
         ctx = tp.sequence_parallel_context(2048, 4096, None, dev)
         from tests import helpers as H
 
         gamma = H.config0_gamma(4096, 3).to(dev)
         res = H.config0_x(2048, 4096, 4).to(dev)[ctx.row_bounds()[0]:ctx.row_bounds()[1]].contiguous()
-        ctx.partial.copy_((0.2 * H.config0_x(2048, 4096, 20 + rank).float()).to(torch.bfloat16).to(dev))
+        ctx.deliver((0.2 * H.config0_x(2048, 4096, 20 + rank).float()).to(torch.bfloat16).to(dev))
         torch.cuda.synchronize()
         dist.barrier()
         prep, new_res = ctx.transition(res, gamma, 1e-6)
@@ -125,16 +147,17 @@ def main():
         if model._sequence_parallel_context(ids.numel()) is None:
             ok = False
             say("the decoder did not take the sequence-parallel path")
-        # reference flow: replicated residual stream with the in-switch all-reduce, which sums the
-        # partial products exactly as the transition kernel does, so the logits must be identical
+        # reference flow: replicated residual stream with the peer-copy all-reduce, which sums the partial
+        # products exactly as the transition kernel does (fp32 in rank order, one rounding), so the logits
+        # must be identical
         os.environ["SHARQ_TP_SEQUENCE_PARALLEL"] = "0"
-        os.environ["SHARQ_TP_ALLREDUCE"] = "multimem"
+        os.environ["SHARQ_TP_ALLREDUCE"] = "peer"
         logits_ar = model.prefill(ids)
         os.environ["SHARQ_TP_SEQUENCE_PARALLEL"] = "1"
         torch.cuda.synchronize()
         ops.check_device_errors()
         rel = float((logits_sp - logits_ar).norm() / logits_ar.norm())
-        say(f"decoder logits: sequence-parallel vs in-switch all-reduce relative difference {rel:.3e}")
+        say(f"decoder logits: sequence-parallel vs peer-copy all-reduce relative difference {rel:.3e}")
         if not (torch.equal(logits_sp, logits_ar) and bool(torch.isfinite(logits_sp).all())):
             ok = False
             say("decoder logits differ between the sequence-parallel and the all-reduce flow")
