@@ -43,6 +43,21 @@ def test_size_queries_and_argument_errors_without_gpu():
     assert rc != 0 and b"beta == 0" in L.sharq_last_error()
     with pytest.raises(_lib.SharqError):
         _lib.check(L.sharq_set_gemm_tile_n(64))
+    # tensor-parallel and grouped entry points reject shapes they cannot split, before any launch
+    rc = L.sharq_tp_reduce_rmsnorm_prepare_allgather(None, None, None, None, 1e-6, 2048 + 128, 0, 4096, None, 0, None, None,
+                                                     None, None, None, 0, None, None, 0, 8, None, None)
+    assert rc != 0 and b"128 * world" in L.sharq_last_error()
+    rc = L.sharq_linear_gemm_scatter(None, None, None, None, None, None, None, None, 2048, 4096, 512, 1.0, None, None, 0, 1,
+                                     None, None)
+    assert rc != 0 and b"world must be in [2" in L.sharq_last_error()
+    rc = L.sharq_linear_gemm_grouped(None, None, None, None, None, 17, None, None, None, None, None, 1.0, 512, 256, 256, None,
+                                     None, None)
+    assert rc != 0 and b"groups must be in [1, 16]" in L.sharq_last_error()
+    rc = L.sharq_grouped_sparse_residual_quantize_x(None, None, 300, 0, 256, None, 4, None, None, None, None, None, None, None,
+                                                    None)
+    assert rc != 0 and b"multiple of 256" in L.sharq_last_error()
+    assert L.sharq_tp_transition_state_bytes() >= 256 and L.sharq_tp_transition_workspace_bytes(256) == 1024
+    assert L.sharq_set_wait_limit_cycles(0) == 0 and L.sharq_set_wait_limit_cycles(-1) != 0
 
 
 def test_ops_reject_cpu_tensors():
