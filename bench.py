@@ -738,8 +738,13 @@ def run_shape_sweep(args):
             x = x.to(torch.bfloat16).to(dev)
             iters = 5 if m >= 2048 else 10
             prep = ops.scaled_sparse_residual_quantize_x(x, n)
-            t_prep = timed(lambda: ops.scaled_sparse_residual_quantize_x(x, n), iters)
-            t_prep_rms = timed(lambda: ops.fused_rmsnorm_sparse_residual_quantize_x(x, gamma, 1e-6, n), iters) if gamma is not None else None
+            # prepares last 10-200 us, about what launching them one by one from Python costs: replay
+            # them from a graph over rotating input copies (inputs + outputs together larger than L2)
+            xc = [x.clone() for _ in range(min(48, max(2, int(300e6 // (2.906 * m * k)) + 1)))]
+            t_prep = timed_rotating(lambda i: (lambda: ops.scaled_sparse_residual_quantize_x(xc[i], n)), len(xc))
+            t_prep_rms = (timed_rotating(lambda i: (lambda: ops.fused_rmsnorm_sparse_residual_quantize_x(xc[i], gamma, 1e-6, n)),
+                                         len(xc)) if gamma is not None else None)
+            del xc
             a_comp, e, sfa, q_res, sf_res, scale = prep
             alpha = float(scale.item())
             xs = (x.float() / scale).to(torch.bfloat16)
@@ -780,7 +785,8 @@ def run_shape_sweep(args):
         del qw, sfs, sfd, qw_d, sfw_d
         torch.cuda.empty_cache()
     print(json.dumps({"sweep": "config 1: SharQ GEMM shape sweep; M >= 2048: cold L2 (256 MB written between launches), "
-                               "M <= 128: GEMMs replayed from a CUDA graph over rotating weight copies larger than L2",
+                               "M <= 128: GEMMs replayed from a CUDA graph over rotating weight copies larger than L2; "
+                               "prepares: replayed from a CUDA graph over rotating input copies larger than L2",
                       "peaks": peaks, "tensor_frac_convention": "3*M*N*K dense-FP4-equivalent / (4 x bf16 sustained)",
                       "rows": rows}), flush=True)
 
