@@ -190,14 +190,18 @@ def run_ours(args):
 
         sp = sequence_parallel_context(m, HIDDEN, None, dev)
     tp_mode = "tp1" if world == 1 else ("sequence-parallel transition kernel" if sp is not None else "all-reduce kernel")
-    rb, re_ = (sp.row_bounds() if sp is not None else (0, m))
     h_full = act(m, HIDDEN)
-    host = {"h": h_full[rb:re_].contiguous().pin_memory(), "o_in": act(m, HIDDEN)[:, ob:oe].contiguous().pin_memory(),
-            "d_in": act(m, FFN)[:, db:de].contiguous().pin_memory()}
-    devx = {k2: v.to(dev) for k2, v in host.items()}
-    out_host = torch.empty((re_ - rb, HIDDEN), dtype=torch.bfloat16).pin_memory()
-    h2d_bytes = sum(v.numel() * 2 for v in host.values())
-    d2h_bytes = out_host.numel() * 2
+    o_in_full, d_in_full = act(m, HIDDEN), act(m, FFN)
+
+    def make_inputs():
+        """Pinned host inputs of this rank for the current flow (the transition flow holds only its
+        own rows of the residual stream), their device copies and the pinned result buffer."""
+        rb, re_ = (sp.row_bounds() if sp is not None else (0, m))
+        host_ = {"h": h_full[rb:re_].contiguous().pin_memory(), "o_in": o_in_full[:, ob:oe].contiguous().pin_memory(),
+                 "d_in": d_in_full[:, db:de].contiguous().pin_memory()}
+        return host_, {k2: v.to(dev) for k2, v in host_.items()}, torch.empty((re_ - rb, HIDDEN), dtype=torch.bfloat16).pin_memory()
+
+    host, devx, out_host = make_inputs()
 
     class Timers:
         """CUDA events around the prepare / transition and GEMM calls of one eager step."""
@@ -284,14 +288,32 @@ def run_ours(args):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    barrier()  # the ranks finish building their layers at different times
-    for _ in range(max(args.warmup, 3)):
-        step(devx)
-    ops.check_device_errors()
+    def agree(ok):
+        """True when every rank says ok (a rank must not enter a collective that another rank skips)."""
+        if world == 1:
+            return ok
+        flag = torch.tensor([1.0 if ok else 0.0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        return float(flag.item()) == 1.0
 
-    # ---- correctness of the cross-GPU step (outside every timed region)
-    tp_check = None
-    if world > 1:
+    def device_errors():
+        try:
+            ops.check_device_errors()
+            return None
+        except RuntimeError as exc:
+            return str(exc)
+
+    def warm_up_and_check():
+        """Warm-up steps, then the correctness check of the cross-GPU step (outside every timed
+        region).  -> (tp_check record or None, None) or (None, reason of the failure)."""
+        barrier()  # the ranks finish building their layers at different times
+        for _ in range(max(args.warmup, 3)):
+            step(devx)
+        err = device_errors()
+        if not agree(err is None):
+            return None, err or "a bounded wait ran out on another rank during the warm-up"
+        if world == 1:
+            return None, None
         lin = layers[0]["down"]
         prep = lin.local.prepare_input(devx["d_in"])
         partial = lin.local.apply_prepared(prep).clone()
@@ -314,23 +336,33 @@ def run_ours(args):
             same = same and torch.equal(prepared[6].reshape(()), single[5].reshape(()))
             good = rel <= 5e-3 and same and bool(torch.isfinite(full).all())
             what = "transition kernel on the down_proj partial products of layer 0"
-            del rows, full, want_rows, single
         else:
             reduced = lin.apply_prepared_reduced(prep).clone()
             rel = float((reduced.float() - want).norm() / want.norm())
             same = None
             good = rel <= 5e-3 and bool(torch.isfinite(reduced).all())
             what = "all-reduced down_proj output of layer 0"
-            del reduced
-        ops.check_device_errors()
-        flag = torch.tensor([1.0 if good else 0.0], device=dev)
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        if float(flag.item()) != 1.0:
-            raise SystemExit(f"tp_check failed on rank {rank}: {what}: relative Frobenius error {rel:.3e} against the fp32 "
-                             f"sum of the partial products, prepared bytes identical to the single-GPU prepare: {same}")
-        tp_check = {"status": "ok", "what": what, "rel_fro_vs_fp32_sum": round(rel, 6), "tolerance": 5e-3,
-                    "prepared_bytes_identical_to_single_gpu": same}
-        del parts, want, partial, prep
+        err = device_errors()
+        if not agree(good and err is None):
+            return None, (f"tp_check failed (rank {rank}: {what}: relative Frobenius error {rel:.3e} against the fp32 sum of "
+                          f"the partial products, prepared bytes identical to the single-GPU prepare: {same}, device errors: {err})")
+        return {"status": "ok", "what": what, "rel_fro_vs_fp32_sum": round(rel, 6), "tolerance": 5e-3,
+                "prepared_bytes_identical_to_single_gpu": same}, None
+
+    tp_check, failure = warm_up_and_check()
+    if failure is not None and sp is not None:
+        # the transition flow did not pass on this machine: measure the replicated all-reduce flow and say so
+        if rank == 0:
+            print(f"bench.py: falling back to the all-reduce flow: {failure}", file=sys.stderr, flush=True)
+        sp = None
+        os.environ["SHARQ_TP_SEQUENCE_PARALLEL"] = "0"
+        tp_mode = "all-reduce kernel (the transition flow failed its check here: " + failure[:200] + ")"
+        host, devx, out_host = make_inputs()
+        tp_check, failure = warm_up_and_check()
+    if failure is not None:
+        raise SystemExit(f"bench.py: {failure}")
+    h2d_bytes = sum(v.numel() * 2 for v in host.values())
+    d2h_bytes = out_host.numel() * 2
 
     # The step is launch-bound on the host once the work is split over several GPUs, so it is
     # captured once into a CUDA graph (kernels, memsets and the NCCL all-reduces) and replayed;
@@ -370,7 +402,7 @@ def run_ours(args):
     main_stream = torch.cuda.current_stream()
     copy_stream = torch.cuda.Stream()
     stage_in = [{k2: torch.empty_like(v) for k2, v in devx.items()} for _ in range(2)]
-    stage_out = [torch.empty((re_ - rb, HIDDEN), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    stage_out = [torch.empty(tuple(out_host.shape), dtype=torch.bfloat16, device=dev) for _ in range(2)]
     in_ready, in_free, out_ready, out_free = ([torch.cuda.Event() for _ in range(2)] for _ in range(4))
 
     def e2e_run(steps):
