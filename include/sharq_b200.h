@@ -125,6 +125,12 @@ int sharq_rope_inplace(void *x_bf16, int rows, int row_stride, int seq_len, int 
 int sharq_scatter_add_scaled(void *out_bf16, const void *y_bf16, const int64_t *rows, const void *w_bf16, int n_rows,
                              int width, void *stream);
 int sharq_swiglu(const void *gate_up_bf16, int rows, int ffn, void *h_bf16, void *stream);
+/* sharq_add_rmsnorm: out[rows, K] = bf16(s * rsqrt(mean(s^2) + eps) * gamma) with s = bf16(x + residual) written to
+ * sum_out (both NULL: s = x); mean and products in float, one rounding per element.  The normalised bf16
+ * activation that the router and the experts of a mixture-of-experts layer both read
+ * (model/qMixtralLayer.py:205-213; the reference calls HuggingFace's RMSNorm module there).  K % 8 == 0, K <= 8192. */
+int sharq_add_rmsnorm(const void *x_bf16, const void *residual_bf16, void *sum_out_bf16, const void *gamma_bf16, float eps,
+                      int rows, int k, void *out_bf16, void *stream);
 int sharq_swiglu_sparse_residual_quantize_x(const void *gate_up_bf16, int m, int n, int k, void *h_bf16,
                                             void *workspace, size_t workspace_bytes, void *a_comp, void *e,
                                             void *sfa_sparse, void *q_res, void *sf_res, float *scale_out,

@@ -59,8 +59,10 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             sys.stderr.write(out)
         if p.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}")
-    cmd = [nvcc, "-shared", "-o", str(LIB_PATH)] + [str(obj_dir / (s + ".o")) for s in SOURCES]
+    tmp = LIB_PATH.with_suffix(".so.tmp")  # linked beside the target and moved into place, so a reader never sees half a file
+    cmd = [nvcc, "-shared", "-o", str(tmp)] + [str(obj_dir / (s + ".o")) for s in SOURCES]
     subprocess.run(cmd, check=True)
+    os.replace(tmp, LIB_PATH)
     return LIB_PATH
 
 

@@ -33,6 +33,7 @@ SIGNATURES = {
     "sharq_rope_inplace": (c_int, [_P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P]),
     "sharq_scatter_add_scaled": (c_int, [_P, _P, _P, _P, c_int, c_int, _P]),
     "sharq_swiglu": (c_int, [_P, c_int, c_int, _P, _P]),
+    "sharq_add_rmsnorm": (c_int, [_P, _P, _P, _P, c_float, c_int, c_int, _P, _P]),
     "sharq_swiglu_sparse_residual_quantize_x": (
         c_int, [_P, c_int, c_int, c_int, _P, _P, c_size_t, _P, _P, _P, _P, _P, _P, _P]),
     "sharq_quantize_w32_shared": (c_int, [_P, c_int, c_int, _P, _P, _P, _P]),

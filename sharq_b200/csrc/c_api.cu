@@ -165,6 +165,19 @@ int sharq_scatter_add_scaled(void *out_bf16, const void *y_bf16, const int64_t *
                     "scatter_add_scaled");
 }
 
+int sharq_add_rmsnorm(const void *x_bf16, const void *residual_bf16, void *sum_out_bf16, const void *gamma_bf16, float eps,
+                      int rows, int k, void *out_bf16, void *stream) {
+  SHARQ_REQUIRE(x_bf16 && gamma_bf16 && out_bf16, "null buffer");
+  SHARQ_REQUIRE((residual_bf16 == nullptr) == (sum_out_bf16 == nullptr), "residual and sum_out go together");
+  SHARQ_REQUIRE(rows >= 0 && k > 0 && k % 8 == 0 && k <= 8192, "rows must be >= 0 and K a multiple of 8, at most 8192, got %d", k);
+  SHARQ_REQUIRE(((reinterpret_cast<uintptr_t>(x_bf16) | reinterpret_cast<uintptr_t>(residual_bf16) |
+                  reinterpret_cast<uintptr_t>(sum_out_bf16) | reinterpret_cast<uintptr_t>(gamma_bf16) |
+                  reinterpret_cast<uintptr_t>(out_bf16)) & 15) == 0, "buffers must be 16-byte aligned");
+  return check_cuda(sharq::run_add_rmsnorm(x_bf16, residual_bf16, sum_out_bf16, gamma_bf16, eps, rows, k, out_bf16,
+                                           as_stream(stream)),
+                    "add_rmsnorm");
+}
+
 int sharq_swiglu(const void *gate_up_bf16, int rows, int ffn, void *h_bf16, void *stream) {
   SHARQ_REQUIRE(gate_up_bf16 && h_bf16, "null buffer");
   SHARQ_REQUIRE(rows > 0 && ffn > 0 && ffn % 8 == 0, "rows must be positive and ffn a positive multiple of 8");

@@ -10,6 +10,10 @@
 //   swiglu_absmax     h = bf16(bf16(silu(gate)) * up) from a merged gate_up activation, plus
 //                     the tensor-wide max|h| the scaled prepare of down_proj needs, so that
 //                     prepare does not have to read h a second time for it
+//   add_rmsnorm       y = bf16(s * rsqrt(mean(s^2) + eps) * gamma) with s = bf16(x + residual)
+//                     (or s = x), products and mean in float: the normalised bf16 activation
+//                     that a mixture-of-experts router and its experts both read
+//                     (model/qMixtralLayer.py:205-213), in one pass instead of six ATen passes
 #include <cuda_bf16.h>
 
 #include <cstdint>
@@ -105,6 +109,86 @@ __device__ __forceinline__ float silu_bf16(float x) {
   float v = fast;
   if (!(fabsf(x) <= 16.0f && t >= 81u)) v = silu_accurate(x);
   return round_bf16(v);
+}
+
+// One CTA walks rows; its 256 threads hold up to four 16-byte vectors of the row each (K <= 8192)
+// between the sum of squares and the scaling, so the row is read once.
+constexpr int kNormThreads = 256;
+constexpr int kNormVecsPerThread = 4;
+
+template <bool kAdd>
+__global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(const __nv_bfloat16 *__restrict__ x,
+                                                                   const __nv_bfloat16 *__restrict__ residual,
+                                                                   __nv_bfloat16 *__restrict__ sum_out,
+                                                                   const __nv_bfloat16 *__restrict__ gamma, float eps,
+                                                                   long long rows, int k, __nv_bfloat16 *__restrict__ out) {
+  __shared__ float warp_sum[kNormThreads / 32];
+  const int vecs = k >> 3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4 *xs = reinterpret_cast<const uint4 *>(x + row * k);
+    uint4 v[kNormVecsPerThread];
+#pragma unroll
+    for (int i = 0; i < kNormVecsPerThread; ++i) {
+      const int j = threadIdx.x + i * kNormThreads;
+      if (j < vecs) v[i] = __ldg(xs + j);
+    }
+    if (kAdd) {
+      const uint4 *rs = reinterpret_cast<const uint4 *>(residual + row * k);
+      uint4 *ss = reinterpret_cast<uint4 *>(sum_out + row * k);
+#pragma unroll
+      for (int i = 0; i < kNormVecsPerThread; ++i) {
+        const int j = threadIdx.x + i * kNormThreads;
+        if (j < vecs) {
+          const uint4 r = __ldg(rs + j);
+          // bf16(x + residual), rounded like the ATen add
+          v[i].x = pack2(__fadd_rn(lo_f(v[i].x), lo_f(r.x)), __fadd_rn(hi_f(v[i].x), hi_f(r.x)));
+          v[i].y = pack2(__fadd_rn(lo_f(v[i].y), lo_f(r.y)), __fadd_rn(hi_f(v[i].y), hi_f(r.y)));
+          v[i].z = pack2(__fadd_rn(lo_f(v[i].z), lo_f(r.z)), __fadd_rn(hi_f(v[i].z), hi_f(r.z)));
+          v[i].w = pack2(__fadd_rn(lo_f(v[i].w), lo_f(r.w)), __fadd_rn(hi_f(v[i].w), hi_f(r.w)));
+          ss[j] = v[i];
+        }
+      }
+    }
+    float sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kNormVecsPerThread; ++i) {
+      const int j = threadIdx.x + i * kNormThreads;
+      if (j < vecs) {
+        const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float a = lo_f(w[t]), b = hi_f(w[t]);
+          sq = __fmaf_rn(a, a, sq);
+          sq = __fmaf_rn(b, b, sq);
+        }
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+    __syncthreads();  // warp_sum may still be read by the previous row
+    if (lane == 0) warp_sum[warp] = sq;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kNormThreads / 32; ++w) total += warp_sum[w];  // same order in every thread
+    const float inv = rsqrtf(total / (float)k + eps);
+    const uint4 *gs = reinterpret_cast<const uint4 *>(gamma);
+    uint4 *os = reinterpret_cast<uint4 *>(out + row * k);
+#pragma unroll
+    for (int i = 0; i < kNormVecsPerThread; ++i) {
+      const int j = threadIdx.x + i * kNormThreads;
+      if (j < vecs) {
+        const uint4 g = __ldg(gs + j);
+        uint4 y;
+        y.x = pack2(__fmul_rn(__fmul_rn(lo_f(v[i].x), inv), lo_f(g.x)), __fmul_rn(__fmul_rn(hi_f(v[i].x), inv), hi_f(g.x)));
+        y.y = pack2(__fmul_rn(__fmul_rn(lo_f(v[i].y), inv), lo_f(g.y)), __fmul_rn(__fmul_rn(hi_f(v[i].y), inv), hi_f(g.y)));
+        y.z = pack2(__fmul_rn(__fmul_rn(lo_f(v[i].z), inv), lo_f(g.z)), __fmul_rn(__fmul_rn(hi_f(v[i].z), inv), hi_f(g.z)));
+        y.w = pack2(__fmul_rn(__fmul_rn(lo_f(v[i].w), inv), lo_f(g.w)), __fmul_rn(__fmul_rn(hi_f(v[i].w), inv), hi_f(g.w)));
+        os[j] = y;
+      }
+    }
+  }
 }
 
 // CTA-wide maximum of a packed |value| accumulator, raised into *amax_bits (may be null).  All 256 threads call it.
@@ -312,6 +396,24 @@ cudaError_t run_scatter_add_scaled(void *out, const void *y, const long long *ro
   scatter_add_scaled_kernel<<<(unsigned)ctas, 256, 0, stream>>>(static_cast<__nv_bfloat16 *>(out),
                                                                 static_cast<const __nv_bfloat16 *>(y), rows,
                                                                 static_cast<const __nv_bfloat16 *>(w), n_rows, width);
+  return cudaGetLastError();
+}
+
+cudaError_t run_add_rmsnorm(const void *x, const void *residual, void *sum_out, const void *gamma, float eps, long long rows,
+                            int k, void *out, cudaStream_t stream) {
+  if (k <= 0 || (k & 7) != 0 || k > 8 * kNormThreads * kNormVecsPerThread) return cudaErrorInvalidValue;
+  long long ctas = (long long)sm_count() * 8;
+  if (ctas > rows) ctas = rows;
+  if (ctas < 1) return cudaSuccess;
+  if (residual != nullptr)
+    add_rmsnorm_kernel<true><<<(unsigned)ctas, kNormThreads, 0, stream>>>(
+        static_cast<const __nv_bfloat16 *>(x), static_cast<const __nv_bfloat16 *>(residual),
+        static_cast<__nv_bfloat16 *>(sum_out), static_cast<const __nv_bfloat16 *>(gamma), eps, rows, k,
+        static_cast<__nv_bfloat16 *>(out));
+  else
+    add_rmsnorm_kernel<false><<<(unsigned)ctas, kNormThreads, 0, stream>>>(
+        static_cast<const __nv_bfloat16 *>(x), nullptr, nullptr, static_cast<const __nv_bfloat16 *>(gamma), eps, rows, k,
+        static_cast<__nv_bfloat16 *>(out));
   return cudaGetLastError();
 }
 

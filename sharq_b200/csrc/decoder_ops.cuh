@@ -26,6 +26,11 @@ cudaError_t run_abs_stats_grouped(const void *x, long long rows, int width, unsi
 cudaError_t run_moe_combine(void *out, const void *y, const int *dest, const long long *selected, const void *w,
                             long long tokens, int top_k, int width, cudaStream_t stream);
 
+// out[rows, k] = bf16(s * rsqrt(mean(s^2) + eps) * gamma), s = bf16(x + residual) stored to sum_out
+// (residual == nullptr: s = x, sum_out unused); K a multiple of 8, at most 8192.
+cudaError_t run_add_rmsnorm(const void *x, const void *residual, void *sum_out, const void *gamma, float eps, long long rows,
+                            int k, void *out, cudaStream_t stream);
+
 // out[rows[i], :] += y[i, :] * w[i] in bf16 (distinct rows; width a multiple of 8).
 cudaError_t run_scatter_add_scaled(void *out, const void *y, const long long *rows, const void *w, long long n_rows,
                                    int width, cudaStream_t stream);

@@ -214,8 +214,15 @@ class SharqDecoderLayer(torch.nn.Module):
         attn2 = attn.transpose(1, 2).reshape(b * s, self.local_heads * cfg.head_dim)
         o = self.o_proj(attn2)
         if cfg.experts > 0:
-            x2 = x2 + o
-            d = self._moe(_rmsnorm(x2, self.post_norm, cfg.eps))
+            if self.fused_glue and h <= 8192:
+                from . import ops
+
+                # residual add + norm in one launch (the router and the experts read hn)
+                hn, x2 = ops.add_rmsnorm(o.contiguous(), self.post_norm, cfg.eps, residual=x2.contiguous())
+            else:
+                x2 = x2 + o
+                hn = _rmsnorm(x2, self.post_norm, cfg.eps)
+            d = self._moe(hn)
             if return_delta:
                 return x2.view(b, s, h), d.view(b, s, h)
             return (x2 + d).view(b, s, h)

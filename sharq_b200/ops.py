@@ -274,6 +274,28 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     return H
 
 
+def add_rmsnorm(X: torch.Tensor, rmsnorm_weight: torch.Tensor, rmsnorm_eps: float, residual: Optional[torch.Tensor] = None):
+    """bf16(S * rsqrt(mean(S^2) + eps) * weight) with S = X + residual (bf16, as the ATen add rounds) or
+    S = X: one launch (mean and products in float, one rounding per element).
+    -> Y, or (Y, S) when a residual is given.  K % 8 == 0, K <= 8192."""
+    _check(X.is_cuda and X.dtype == torch.bfloat16 and X.dim() == 2 and X.is_contiguous(),
+           "X must be a contiguous CUDA bfloat16 matrix")
+    M, K = int(X.shape[0]), int(X.shape[1])
+    _check(K % 8 == 0 and K <= 8192, f"add_rmsnorm requires K to be a multiple of 8, at most 8192, got {K}")
+    _check(rmsnorm_weight.is_cuda and rmsnorm_weight.dtype == torch.bfloat16 and rmsnorm_weight.is_contiguous()
+           and rmsnorm_weight.numel() == K and rmsnorm_weight.device == X.device, "rmsnorm_weight must be bfloat16 [K] on X's device")
+    if residual is not None:
+        _check(residual.is_cuda and residual.dtype == torch.bfloat16 and residual.is_contiguous()
+               and residual.shape == X.shape and residual.device == X.device, "residual must match X")
+    Y = torch.empty_like(X)
+    S = torch.empty_like(X) if residual is not None else None
+    with _on_device(X.device):
+        _lib.check(_lib.lib().sharq_add_rmsnorm(_ptr(X), _ptr(residual) if residual is not None else None,
+                                                _ptr(S) if S is not None else None, _ptr(rmsnorm_weight), float(rmsnorm_eps),
+                                                M, K, _ptr(Y), _stream(X.device)))
+    return Y if residual is None else (Y, S)
+
+
 def swiglu_sparse_residual_quantize_x(gate_up: torch.Tensor, N: int):
     """silu(gate) * up followed by the scaled prepare of the product, for down_proj:
     -> (A_comp, E, SFA_sparse, Q_res, SF_res, scale).  Equals

@@ -56,6 +56,13 @@ def test_size_queries_and_argument_errors_without_gpu():
     rc = L.sharq_grouped_sparse_residual_quantize_x(None, None, 300, 0, 256, None, 4, None, None, None, None, None, None, None,
                                                     None)
     assert rc != 0 and b"multiple of 256" in L.sharq_last_error()
+    import ctypes
+
+    one = ctypes.c_void_p(256)  # any non-null aligned address: the checks below fail before it is used
+    rc = L.sharq_add_rmsnorm(one, None, None, one, 1e-6, 4, 8200, one, None)
+    assert rc != 0 and b"at most 8192" in L.sharq_last_error()
+    rc = L.sharq_add_rmsnorm(one, one, None, one, 1e-6, 4, 4096, one, None)
+    assert rc != 0 and b"go together" in L.sharq_last_error()
     assert L.sharq_tp_transition_state_bytes() >= 256 and L.sharq_tp_transition_workspace_bytes(256) == 1024
     assert L.sharq_set_wait_limit_cycles(0) == 0 and L.sharq_set_wait_limit_cycles(-1) != 0
 

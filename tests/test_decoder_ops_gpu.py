@@ -103,3 +103,34 @@ def test_scatter_add_scaled_equals_aten():
     want = out0.clone().index_add_(0, rows, y * w[:, None])
     got = ops.scatter_add_scaled_(out0.clone(), y, rows, w)
     assert torch.equal(got, want)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,k,with_residual", [(300, 4096, True), (64, 3584, True), (17, 8192, False), (1, 128, False)])
+def test_add_rmsnorm_equals_the_float_composition(rows, k, with_residual):
+    """bf16(S * rsqrt(mean(S^2) + eps) * gamma), S = bf16(x + residual): the sum S is bit-equal to the
+    ATen add; the normalised values equal the float composition except where the order of the
+    float sum of squares moves a value across a bf16 rounding boundary (at most one bf16 ulp, rare)."""
+    from sharq_b200 import ops
+
+    g = torch.Generator().manual_seed(rows + k)
+    x = torch.randn(rows, k, generator=g).to(torch.bfloat16).cuda()
+    x[:, :: 97] *= 20.0
+    r = torch.randn(rows, k, generator=g).to(torch.bfloat16).cuda() if with_residual else None
+    gamma = (1 + 0.1 * torch.randn(k, generator=g)).to(torch.bfloat16).cuda()
+    eps = 1e-5
+    if with_residual:
+        y, s = ops.add_rmsnorm(x, gamma, eps, residual=r)
+        assert torch.equal(s, x + r)
+    else:
+        y = ops.add_rmsnorm(x, gamma, eps)
+        s = x
+    sd = s.double()
+    want64 = sd * torch.rsqrt(sd.pow(2).mean(-1, keepdim=True) + eps) * gamma.double()
+    sf = s.float()
+    want = (sf * torch.rsqrt(sf.pow(2).mean(-1, keepdim=True) + eps) * gamma.float()).to(torch.bfloat16)
+    differing = (y != want).float().mean().item()
+    assert differing <= 2e-3, differing
+    # never further than one bf16 spacing (2^-8 relative) plus float noise from the exact value
+    err = (y.double() - want64).abs()
+    assert bool((err <= want64.abs() * 2.0 ** -8 + 1e-30).all())
