@@ -218,8 +218,12 @@ struct PrepareParams {
 constexpr int kPrepareCtasPerSm = 3;
 constexpr size_t kInlineAbsmaxElements = 256 * 1024;  // up to 512 KB of input is scanned by every CTA
 
-template <int kMode, bool kDebug>
-__global__ void __launch_bounds__(kPrepareThreads, kPrepareCtasPerSm) prepare_kernel(const PrepareParams p) {
+// kCtas: resident CTAs per SM the register allocation aims at.  The tensor-scale mode runs
+// fastest with two (no spills) except on a gathered, grouped activation, where the third CTA
+// hides more of the gather's latency (measured: 2048 x 14336 43.3 -> 41.1 us with two,
+// 34816 x 4096 grouped 253 -> 264 us).
+template <int kMode, bool kDebug, int kCtas = kPrepareCtasPerSm>
+__global__ void __launch_bounds__(kPrepareThreads, kCtas) prepare_kernel(const PrepareParams p) {
   const int m = p.m, k = p.k;
   const int groups32 = k >> 5;
   const int aligned_m = (m + 127) / 128 * 128;
@@ -364,7 +368,19 @@ __global__ void __launch_bounds__(kPrepareThreads, kPrepareCtasPerSm) prepare_ke
           }
         }
       }
-      scale_quantize_group<kMode, kDebug>(xw, t_scale, t_recip, tbl, o);
+      scale_quantize_group<kMode, kDebug>(xw, t_scale, t_recip, tbl, o, [&](uint32_t (&w)[16]) {
+        // mode 2, rare: the group is read again for the division form
+        const int in_row = p.src_row != nullptr ? p.src_row[row] : row;
+        const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (size_t)in_row * k + (size_t)group * 32);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint4 v = __ldg(src + j);
+          w[4 * j + 0] = v.x;
+          w[4 * j + 1] = v.y;
+          w[4 * j + 2] = v.z;
+          w[4 * j + 3] = v.w;
+        }
+      });
 
       uint4 q = make_uint4(o.q_res[0], o.q_res[1], o.q_res[2], o.q_res[3]);
       *reinterpret_cast<uint4 *>(p.q_res + (size_t)row * (k / 2) + (size_t)group * 16) = q;
@@ -699,16 +715,17 @@ __global__ void __launch_bounds__(kFusedThreads, 1) prepare_fused_kernel(const F
       o.sf_res = 0;
 #pragma unroll
       for (int i = 0; i < 4; ++i) o.q_res[i] = o.q_sparse[i] = 0;
-      if (live) {
+      // the group's 32 values from the row cache or, for a chunk that is not cached, from global memory
+      auto load_group = [&](uint32_t (&w)[16]) {
         if (cached) {
           const uint4 *row_cache = cache + (size_t)rl * row_vecs;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const uint4 v = row_cache[cache_slot(group, j)];
-            xw[4 * j + 0] = v.x;
-            xw[4 * j + 1] = v.y;
-            xw[4 * j + 2] = v.z;
-            xw[4 * j + 3] = v.w;
+            w[4 * j + 0] = v.x;
+            w[4 * j + 1] = v.y;
+            w[4 * j + 2] = v.z;
+            w[4 * j + 3] = v.w;
           }
         } else {
           // plain loads: with kAdd these bytes were written by this CTA in phase 1
@@ -716,11 +733,16 @@ __global__ void __launch_bounds__(kFusedThreads, 1) prepare_fused_kernel(const F
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const uint4 v = xs[j];
-            xw[4 * j + 0] = v.x;
-            xw[4 * j + 1] = v.y;
-            xw[4 * j + 2] = v.z;
-            xw[4 * j + 3] = v.w;
+            w[4 * j + 0] = v.x;
+            w[4 * j + 1] = v.y;
+            w[4 * j + 2] = v.z;
+            w[4 * j + 3] = v.w;
           }
+        }
+      };
+      if (live) {
+        load_group(xw);
+        if (!cached) {
           if (kMode == 1) {
             const float inv = inv_s[chunk_first_row(c) + rl];
 #pragma unroll
@@ -736,7 +758,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) prepare_fused_kernel(const F
             }
           }
         }
-        scale_quantize_group<kMode, false>(xw, div, recip, tbl, o);
+        scale_quantize_group<kMode, false>(xw, div, recip, tbl, o, load_group);
       }
       store_group(p, o, row, group, live, group < groups_padded, aligned_m, lane);
     }
@@ -789,8 +811,10 @@ static cudaError_t launch_prepare(int mode, bool debug, const PrepareParams &p, 
       attr_set[dev] = true;
     }
     prepare_kernel<1, false><<<grid, block, gamma_bytes, stream>>>(p);
-  } else {
+  } else if (p.unit_group != nullptr) {
     prepare_kernel<2, false><<<grid, block, 0, stream>>>(p);
+  } else {
+    prepare_kernel<2, false, 2><<<grid, block, 0, stream>>>(p);
   }
   return cudaGetLastError();
 }
@@ -888,7 +912,13 @@ cudaError_t run_scaled_prepare(const void *x, const void *gamma, float eps, int 
   const bool rms = gamma != nullptr;
   // a small non-RMSNorm input (a decode step): the prepare kernel finds max|x| itself
   const bool inline_absmax = !rms && !absmax_ready && (size_t)m * k <= kInlineAbsmaxElements;
-  if (!absmax_ready && !inline_absmax && fused_prepare_enabled()) {
+  // One cooperative launch pays while the per-SM row caches hold most of the tensor; beyond that
+  // the separate statistics and prepare kernels (more resident warps per SM) are faster.  Measured
+  // crossovers (us, one launch / separate): RMSNorm 4096 x 4096 35.0 / 37.0, 8192 x 4096
+  // 65.7 / 63.8, 16384 x 4096 136 / 118; tensor scale 2048 x 7168 24.9 / 25.0, 4096 x 4096 28.7 / 27.0.
+  const size_t elements = (size_t)m * (size_t)k;
+  const bool one_launch_pays = elements < (rms ? ((size_t)1 << 25) : ((size_t)1 << 24));
+  if (!absmax_ready && !inline_absmax && one_launch_pays && fused_prepare_enabled()) {
     FusedParams f{};
     f.x = static_cast<const __nv_bfloat16 *>(x);
     f.residual = static_cast<const __nv_bfloat16 *>(residual);

@@ -209,24 +209,26 @@ __device__ __forceinline__ float round_to_bf16(float x) { return __bfloat162floa
 //            the same bf16 as the IEEE quotient, no test needed.  The argument needs a normal
 //            quotient; subnormal quotients only matter when such a value takes part in a pair
 //            selection, which the keys show (second_min): that group is redone with divisions.
-template <int kMode, bool kDebug>
+//            The retry reads the group again through `reload` instead of keeping a second copy
+//            of it in registers across the quantisation.
+template <int kMode, bool kDebug, typename Reload>
 __device__ __forceinline__ void scale_quantize_group(uint32_t (&y)[16], float div, float recip, const ScaleTables &tbl,
-                                                     GroupOut &o) {
+                                                     GroupOut &o, Reload reload) {
   if (kMode == 1) {
     scale_group32(y, div, recip);
     quantize_group32<kDebug>(y, tbl, o);
   } else if (kMode == 2) {
-    uint32_t q[16];
 #pragma unroll 1
     for (int attempt = 0; attempt < 2; ++attempt) {
       if (attempt == 0) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) q[i] = pack_bf16x2(__fmul_rn(lo_f(y[i]), recip), __fmul_rn(hi_f(y[i]), recip));
+        for (int i = 0; i < 16; ++i) y[i] = pack_bf16x2(__fmul_rn(lo_f(y[i]), recip), __fmul_rn(hi_f(y[i]), recip));
       } else {
+        reload(y);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) q[i] = pack_bf16x2(__fdiv_rn(lo_f(y[i]), div), __fdiv_rn(hi_f(y[i]), div));
+        for (int i = 0; i < 16; ++i) y[i] = pack_bf16x2(__fdiv_rn(lo_f(y[i]), div), __fdiv_rn(hi_f(y[i]), div));
       }
-      quantize_group32<kDebug>(q, tbl, o);
+      quantize_group32<kDebug>(y, tbl, o);
       if (o.second_min >= kTinyKey) break;
     }
   } else {

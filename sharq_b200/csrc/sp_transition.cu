@@ -383,7 +383,7 @@ __global__ void __launch_bounds__(kThreads, 1) sp_transition_kernel(const SpPara
                                           __fmul_rn(__fmul_rn(hi_f(vw[q]), inv), hi_f(gw[q])));
           }
         }
-        scale_quantize_group<1, false>(xw, scale, recip, tbl, o);
+        scale_quantize_group<1, false>(xw, scale, recip, tbl, o, [](uint32_t (&)[16]) {});  // mode 1 never reloads
         *reinterpret_cast<uint4 *>(p.q_res + (size_t)row * (k / 2) + (size_t)group * 16) =
             make_uint4(o.q_res[0], o.q_res[1], o.q_res[2], o.q_res[3]);
         *reinterpret_cast<uint2 *>(p.a_comp + (size_t)row * (k / 4) + (size_t)group * 8) = make_uint2(o.a_comp[0], o.a_comp[1]);
