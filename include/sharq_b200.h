@@ -121,9 +121,10 @@ int sharq_rope_inplace(void *x_bf16, int rows, int row_stride, int seq_len, int 
                        const void *cos_bf16, const void *sin_bf16, void *stream);
 /* sharq_scatter_add_scaled: out[rows[i], :] += y[i, :] * w[i] in bf16 with the roundings of
  * `final.index_add_(0, rows, y * w[:, None])` (the expert loop of model/qMixtralLayer.py:228-231);
- * out [*, width] and y [n_rows, width] contiguous bf16, rows int64 and pairwise distinct, w bf16. */
-int sharq_scatter_add_scaled(void *out_bf16, const void *y_bf16, const int64_t *rows, const void *w_bf16, int n_rows,
-                             int width, void *stream);
+ * out [out_rows, width] and y [n_rows, width] contiguous bf16, rows int64 and pairwise distinct, w bf16;
+ * an index outside [0, out_rows) is skipped. */
+int sharq_scatter_add_scaled(void *out_bf16, int out_rows, const void *y_bf16, const int64_t *rows, const void *w_bf16,
+                             int n_rows, int width, void *stream);
 int sharq_swiglu(const void *gate_up_bf16, int rows, int ffn, void *h_bf16, void *stream);
 /* sharq_add_rmsnorm: out[rows, K] = bf16(s * rsqrt(mean(s^2) + eps) * gamma) with s = bf16(x + residual) written to
  * sum_out (both NULL: s = x); mean and products in float, one rounding per element.  The normalised bf16

@@ -31,7 +31,7 @@ SIGNATURES = {
     "sharq_fused_add_rmsnorm_sparse_residual_quantize_x": (
         c_int, [_P, _P, _P, _P, c_float, c_int, c_int, c_int, _P, c_size_t, _P, _P, _P, _P, _P, _P, _P]),
     "sharq_rope_inplace": (c_int, [_P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P]),
-    "sharq_scatter_add_scaled": (c_int, [_P, _P, _P, _P, c_int, c_int, _P]),
+    "sharq_scatter_add_scaled": (c_int, [_P, c_int, _P, _P, _P, c_int, c_int, _P]),
     "sharq_swiglu": (c_int, [_P, c_int, c_int, _P, _P]),
     "sharq_add_rmsnorm": (c_int, [_P, _P, _P, _P, c_float, c_int, c_int, _P, _P]),
     "sharq_swiglu_sparse_residual_quantize_x": (

@@ -154,14 +154,15 @@ int sharq_rope_inplace(void *x_bf16, int rows, int row_stride, int seq_len, int 
                     "rope_inplace");
 }
 
-int sharq_scatter_add_scaled(void *out_bf16, const void *y_bf16, const int64_t *rows, const void *w_bf16, int n_rows,
-                             int width, void *stream) {
+int sharq_scatter_add_scaled(void *out_bf16, int out_rows, const void *y_bf16, const int64_t *rows, const void *w_bf16,
+                             int n_rows, int width, void *stream) {
   SHARQ_REQUIRE(out_bf16 && y_bf16 && rows && w_bf16, "null buffer");
-  SHARQ_REQUIRE(n_rows >= 0 && width > 0 && width % 8 == 0, "n_rows must be >= 0 and width a positive multiple of 8");
+  SHARQ_REQUIRE(n_rows >= 0 && out_rows >= 0 && width > 0 && width % 8 == 0,
+                "n_rows and out_rows must be >= 0 and width a positive multiple of 8");
   SHARQ_REQUIRE(((reinterpret_cast<uintptr_t>(out_bf16) | reinterpret_cast<uintptr_t>(y_bf16)) & 15) == 0,
                 "out and y must be 16-byte aligned");
   return check_cuda(sharq::run_scatter_add_scaled(out_bf16, y_bf16, reinterpret_cast<const long long *>(rows), w_bf16,
-                                                  n_rows, width, as_stream(stream)),
+                                                  n_rows, width, out_rows, as_stream(stream)),
                     "scatter_add_scaled");
 }
 

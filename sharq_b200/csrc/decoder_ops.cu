@@ -337,17 +337,19 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(__nv_bfloat16 *__restr
 // Expert output back into the token-major buffer of a mixture-of-experts layer:
 // out[rows[i], :] = bf16(out[rows[i], :] + bf16(y[i, :] * w[i])), rounded like the ATen
 // `index_add_(0, rows, y * w[:, None])`.  A token reaches an expert at most once, so the rows of
-// one call are distinct and no atomics are needed.
+// one call are distinct and no atomics are needed.  An index outside [0, out_rows) is skipped.
 __global__ void __launch_bounds__(256) scatter_add_scaled_kernel(__nv_bfloat16 *__restrict__ out,
                                                                  const __nv_bfloat16 *__restrict__ y,
                                                                  const long long *__restrict__ rows,
                                                                  const __nv_bfloat16 *__restrict__ w, long long n_rows,
-                                                                 int width) {
+                                                                 int width, long long out_rows) {
   const int vecs = width >> 3;
   for (long long r = blockIdx.x; r < n_rows; r += gridDim.x) {
+    const long long target = rows[r];
+    if (target < 0 || target >= out_rows) continue;
     const float wr = __bfloat162float(w[r]);
     const uint4 *src = reinterpret_cast<const uint4 *>(y + r * (long long)width);
-    uint4 *dst = reinterpret_cast<uint4 *>(out + rows[r] * (long long)width);
+    uint4 *dst = reinterpret_cast<uint4 *>(out + target * (long long)width);
     for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
       const uint4 a4 = __ldg(src + v);
       const uint4 o4 = dst[v];
@@ -389,13 +391,13 @@ cudaError_t run_rope_inplace(void *x, long long rows, long long row_stride, int 
 }
 
 cudaError_t run_scatter_add_scaled(void *out, const void *y, const long long *rows, const void *w, long long n_rows,
-                                   int width, cudaStream_t stream) {
+                                   int width, long long out_rows, cudaStream_t stream) {
   long long ctas = (long long)sm_count() * 8;
   if (ctas > n_rows) ctas = n_rows;
   if (ctas < 1) return cudaSuccess;
   scatter_add_scaled_kernel<<<(unsigned)ctas, 256, 0, stream>>>(static_cast<__nv_bfloat16 *>(out),
                                                                 static_cast<const __nv_bfloat16 *>(y), rows,
-                                                                static_cast<const __nv_bfloat16 *>(w), n_rows, width);
+                                                                static_cast<const __nv_bfloat16 *>(w), n_rows, width, out_rows);
   return cudaGetLastError();
 }
 

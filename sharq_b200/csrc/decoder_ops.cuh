@@ -31,8 +31,8 @@ cudaError_t run_moe_combine(void *out, const void *y, const int *dest, const lon
 cudaError_t run_add_rmsnorm(const void *x, const void *residual, void *sum_out, const void *gamma, float eps, long long rows,
                             int k, void *out, cudaStream_t stream);
 
-// out[rows[i], :] += y[i, :] * w[i] in bf16 (distinct rows; width a multiple of 8).
+// out[rows[i], :] += y[i, :] * w[i] in bf16 (distinct rows inside [0, out_rows), others skipped; width a multiple of 8).
 cudaError_t run_scatter_add_scaled(void *out, const void *y, const long long *rows, const void *w, long long n_rows,
-                                   int width, cudaStream_t stream);
+                                   int width, long long out_rows, cudaStream_t stream);
 
 }  // namespace sharq

@@ -246,7 +246,7 @@ def rope_inplace_(qkv: torch.Tensor, heads: int, head_dim: int, cos: torch.Tenso
 
 def scatter_add_scaled_(out: torch.Tensor, y: torch.Tensor, rows: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """out[rows[i]] += y[i] * w[i] (bf16, rows int64 and distinct): `out.index_add_(0, rows, y * w[:, None])`
-    of the mixture-of-experts loop in one pass."""
+    of the mixture-of-experts loop in one pass.  An index outside out's rows is skipped."""
     _check(out.is_cuda and out.dtype == torch.bfloat16 and out.dim() == 2 and out.is_contiguous(),
            "out must be a contiguous CUDA bfloat16 matrix")
     _check(y.is_cuda and y.dtype == torch.bfloat16 and y.dim() == 2 and y.is_contiguous() and y.shape[1] == out.shape[1],
@@ -257,8 +257,8 @@ def scatter_add_scaled_(out: torch.Tensor, y: torch.Tensor, rows: torch.Tensor, 
            "w must be a contiguous CUDA bfloat16 vector with one entry per row of y")
     _check(out.shape[1] % 8 == 0, "width must be a multiple of 8")
     with _on_device(out.device):
-        _lib.check(_lib.lib().sharq_scatter_add_scaled(_ptr(out), _ptr(y), _ptr(rows), _ptr(w), int(y.shape[0]),
-                                                       int(out.shape[1]), _stream(out.device)))
+        _lib.check(_lib.lib().sharq_scatter_add_scaled(_ptr(out), int(out.shape[0]), _ptr(y), _ptr(rows), _ptr(w),
+                                                       int(y.shape[0]), int(out.shape[1]), _stream(out.device)))
     return out
 
 

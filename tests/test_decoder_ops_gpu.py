@@ -103,6 +103,11 @@ def test_scatter_add_scaled_equals_aten():
     want = out0.clone().index_add_(0, rows, y * w[:, None])
     got = ops.scatter_add_scaled_(out0.clone(), y, rows, w)
     assert torch.equal(got, want)
+    # indices outside the output are skipped, the other rows are still added
+    bad = rows.clone()
+    bad[0], bad[1] = -1, 1000
+    want = out0.clone().index_add_(0, rows[2:], (y * w[:, None])[2:])
+    assert torch.equal(ops.scatter_add_scaled_(out0.clone(), y, bad, w), want)
 
 
 @pytest.mark.gpu
