@@ -219,7 +219,7 @@ constexpr int kPrepareCtasPerSm = 3;
 constexpr size_t kInlineAbsmaxElements = 256 * 1024;  // up to 512 KB of input is scanned by every CTA
 
 // kCtas: resident CTAs per SM the register allocation aims at.  The tensor-scale mode runs
-// fastest with two (no spills) except on a gathered, grouped activation, where the third CTA
+// fastest with two (no spills) except on a gathered activation (src_row), where the third CTA
 // hides more of the gather's latency (measured: 2048 x 14336 43.3 -> 41.1 us with two,
 // 34816 x 4096 grouped 253 -> 264 us).
 template <int kMode, bool kDebug, int kCtas = kPrepareCtasPerSm>
@@ -811,7 +811,7 @@ static cudaError_t launch_prepare(int mode, bool debug, const PrepareParams &p, 
       attr_set[dev] = true;
     }
     prepare_kernel<1, false><<<grid, block, gamma_bytes, stream>>>(p);
-  } else if (p.unit_group != nullptr) {
+  } else if (p.src_row != nullptr) {
     prepare_kernel<2, false><<<grid, block, 0, stream>>>(p);
   } else {
     prepare_kernel<2, false, 2><<<grid, block, 0, stream>>>(p);
