@@ -186,3 +186,42 @@ def test_prepare_rejects_bad_k():
         ops.fused_sparse_residual_quantize_x(torch.zeros(4, 128, device="cuda"), 64)
     with pytest.raises(RuntimeError, match="CUDA tensor"):
         ops.fused_sparse_residual_quantize_x(torch.zeros(4, 128, dtype=torch.bfloat16), 64)
+
+
+_DIGEST_SNIPPET = """
+import hashlib, sys, torch
+sys.path.insert(0, {root!r})
+from sharq_b200 import ops
+from tests import helpers as H
+h = hashlib.sha1()
+for m, k in ((1024, 4096), (300, 14336)):
+    x = H.config0_x(m, k, 21).cuda(); r = H.config0_x(m, k, 22).cuda(); g = H.config0_gamma(k, 21).cuda()
+    outs = list(ops.fused_rmsnorm_sparse_residual_quantize_x(x, g, 1e-6, 4096))
+    outs += list(ops.fused_add_rmsnorm_sparse_residual_quantize_x(x, r, g, 1e-6, 4096))
+    outs += list(ops.scaled_sparse_residual_quantize_x(x, 4096))
+    for t in outs:
+        t = t.reshape(-1) if t.dim() else t.reshape(1)
+        h.update(t.view(torch.uint8).cpu().numpy().tobytes())
+ops.check_device_errors()
+print("DIGEST", h.hexdigest())
+"""
+
+
+def test_one_launch_and_separate_kernels_give_the_same_bytes():
+    """The scaled prepares run as one cooperative launch for small tensors and as statistics +
+    prepare kernels for large ones (or when SHARQ_PREPARE_FUSED=0): both must produce the same
+    bytes.  The switch is read once per process, so each variant runs in its own interpreter."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = str(Path(__file__).resolve().parents[1])
+    digests = []
+    for fused in ("1", "0"):
+        env = dict(os.environ, SHARQ_PREPARE_FUSED=fused)
+        out = subprocess.run([sys.executable, "-c", _DIGEST_SNIPPET.format(root=root)], env=env, capture_output=True,
+                             text=True, timeout=300)
+        assert out.returncode == 0, out.stderr[-2000:]
+        digests.append([l for l in out.stdout.splitlines() if l.startswith("DIGEST")][-1])
+    assert digests[0] == digests[1]
