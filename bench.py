@@ -129,7 +129,35 @@ def kernel_breakdown(fn, reps: int = 2, top: int = 14):
     total = sum(v[1] for v in rows.values()) or 1.0
     out = [{"kernel": k[:90], "launches_per_step": round(v[0] / reps, 1), "us_per_step": round(v[1] / reps, 1),
             "share": round(v[1] / total, 4)} for k, v in sorted(rows.items(), key=lambda kv: -kv[1][1])]
-    return {"kernel_us_per_step": round(total / reps, 1), "rows": out[:top]}
+    cats = {}
+    for k, v in rows.items():
+        c = kernel_category(k)
+        cats[c] = cats.get(c, 0.0) + v[1]
+    categories = {c: {"us_per_step": round(t / reps, 1), "share": round(t / total, 4)}
+                  for c, t in sorted(cats.items(), key=lambda kv: -kv[1])}
+    return {"kernel_us_per_step": round(total / reps, 1), "categories": categories, "rows": out[:top]}
+
+
+def kernel_category(name: str) -> str:
+    """The categories of the reference's prefill profiler (benchmarks/e2e/profile_prefill_nvtx.py:159-275: gemm,
+    sharq_kernel = the activation prepare, quantize_kernel = dense quantisation, attention, rmsnorm), by kernel
+    name; plus `collective` and `other` (rotary embedding, SwiGLU, copies, routing)."""
+    n = name.lower()
+    if "sp_transition" in n:
+        return "sharq_kernel+collective"  # reduce-scatter sum, RMSNorm prepare and all-gather in one kernel
+    if "allreduce" in n or "nccl" in n:
+        return "collective"
+    if "gemm" in n or "splitk_finalize" in n or "nvjet" in n or "cutlass" in n or "cublas" in n:
+        return "gemm"
+    if "prepare_" in n or "rms_stats" in n or "abs_stats" in n:
+        return "sharq_kernel"
+    if "quantize_" in n or "compress_sparse" in n:
+        return "quantize_kernel"
+    if "sdpa" in n or "flash" in n or "fmha" in n:
+        return "attention"
+    if "rmsnorm" in n:
+        return "rmsnorm"
+    return "other"
 
 
 def run_ours(args):
