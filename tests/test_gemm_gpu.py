@@ -123,10 +123,13 @@ def test_gemm_argument_errors():
 
 
 @pytest.mark.parametrize("m,n,k", [(16, 6144, 4096), (128, 4096, 14336), (100, 1000, 1024), (1, 4096, 4096)])
-def test_small_m_split_k_agrees_with_single_pass(m, n, k, monkeypatch):
+def test_small_m_split_k_agrees_with_single_pass(oracle, m, n, k, monkeypatch):
     """M <= 128 with caller scratch: K split over the SMs (fp32 vector reductions + a finalize
-    kernel with alpha / beta / bias) against the same GEMM computed in one pass per tile."""
+    kernel with alpha / beta / bias) against the same GEMM computed in one pass per tile, and
+    both against the float32 product of the dequantised operands (plain PyTorch index
+    arithmetic, no kernel of this project) at the real decode-step shapes."""
     from sharq_b200 import ops
+    from tests.test_fullsize_gpu import _dequant_dense, _dequant_sparse
 
     g = torch.Generator().manual_seed(m + n + k)
     x = torch.randn(m, k, generator=g)
@@ -151,3 +154,12 @@ def test_small_m_split_k_agrees_with_single_pass(m, n, k, monkeypatch):
         assert torch.isfinite(a.float()).all()
         rel = float((a.float() - b.float()).norm() / b.float().norm())
         assert rel <= 2e-3, rel
+    torch.backends.cuda.matmul.allow_tf32 = False
+    xs = _dequant_sparse(a_comp, e, sfa, m, k, oracle)
+    xr = _dequant_dense(q_res, sf_res, 16, oracle)
+    wd = _dequant_dense(qw, sfs, 32, oracle)
+    ref = ((xs + xr) @ wd.T) * alpha + bias.float()
+    for y in (split[0], whole[0]):
+        assert float((y.float() - ref).norm() / ref.norm()) <= TOL
+    ref_sparse = (xs @ wd.T) * alpha
+    assert float((split[1].float() - ref_sparse).norm() / ref_sparse.norm()) <= TOL
