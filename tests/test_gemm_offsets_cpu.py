@@ -60,3 +60,42 @@ def test_bulk_copies_stay_inside_the_buffers(bn, pair):
         size = _sizes(m, n, k)
         for name, off, nbytes in _producer_reads(m, n, k, bn, pair):
             assert off >= 0 and off + nbytes <= size[name], (name, m, n, k, bn, pair, off, nbytes, size[name])
+
+
+@pytest.mark.parametrize("cols_per_warp", [64, 128])
+def test_scatter_epilogue_stages_and_stores_every_piece_once(cols_per_warp):
+    """The scatter-mode epilogue of gemm.cu, restated: a warp owns 32 rows x cols_per_warp columns; per
+    pass it stages 64 columns of 16 rows (lane l of the active half writes its row's eight 16-byte
+    chunks c at slot c ^ (row & 7) of a 128-byte shared-memory row), then every lane reads chunk
+    (lane & 7) of row it*4 + (lane >> 3) and stores it.  Every (row, 16-byte chunk) of the warp's
+    block must be written to shared memory once and stored once, from the slot it was written to,
+    and a store instruction must cover 4 rows x 128 contiguous bytes."""
+    stored = {}
+    for c in range(cols_per_warp // 64):
+        for hrow in range(2):
+            stage = {}
+            for lane in range(32):
+                if lane >> 4 != hrow:
+                    continue
+                srow = lane & 15
+                for chunk_base in (0, 4):
+                    for v in range(4):
+                        slot = (srow, (chunk_base + v) ^ (srow & 7))
+                        assert slot not in stage
+                        stage[slot] = (lane, 64 * c + 8 * (chunk_base + v))  # (row in the warp's block, first column)
+            assert len(stage) == 16 * 8
+            for it in range(4):
+                pieces = []
+                for lane in range(32):
+                    r = it * 4 + (lane >> 3)
+                    src_row, col = stage[(r, (lane & 7) ^ (r & 7))]
+                    grow, gcol = 16 * hrow + r, 64 * c + (lane & 7) * 8
+                    assert (src_row, col) == (grow, gcol)  # the piece read back is the one that belongs there
+                    assert (grow, gcol) not in stored
+                    stored[(grow, gcol)] = True
+                    pieces.append((grow, gcol))
+                for q in range(4):  # each quarter-warp: one row, eight consecutive 16-byte pieces = 128 bytes
+                    rows = {p[0] for p in pieces[8 * q:8 * q + 8]}
+                    cols = [p[1] for p in pieces[8 * q:8 * q + 8]]
+                    assert len(rows) == 1 and cols == list(range(cols[0], cols[0] + 64, 8))
+    assert len(stored) == 32 * (cols_per_warp // 8)
