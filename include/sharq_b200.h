@@ -290,13 +290,15 @@ int sharq_moe_combine(void *out_bf16, const void *y_bf16, const int *dest, const
  *         (partial_blocks == NULL: X' = residual_in; residual_in == NULL: X' = S),
  *   then RMSNorm statistics of X', the tensor scale from the absmax over ALL GPUs' rows, the
  *   4:8 sparse + residual prepare of this GPU's rows, and the packed rows stored into EVERY
- *   GPU's copy of the prepared activation (multimem.st).
+ *   GPU's copy of the prepared activation (plain peer stores; multimem.st with SHARQ_TP_ALLGATHER=multicast).
  * On return of the kernel every GPU's (a_comp, e, sfa_sparse, q_res, sf_res, *scale_out) hold
  * exactly what sharq_fused_rmsnorm_sparse_residual_quantize_x produces for the whole [M,K]
  * matrix X' on one GPU.  The five output buffers are this GPU's copy inside ONE symmetric
  * allocation whose multicast mapping is at local address + multicast_delta; rank_state_ptrs[r]
- * is GPU r's state block (sharq_tp_transition_state_bytes() bytes, in symmetric memory,
- * zero-filled once, then owned by these calls) as mapped on this GPU.  workspace:
+ * is GPU r's state block (sharq_tp_transition_state_bytes() bytes inside the SAME symmetric
+ * allocation, zero-filled once, then owned by these calls) as mapped on this GPU: the kernel
+ * reaches GPU r's copy of an output byte at its local address + (rank_state_ptrs[r] -
+ * rank_state_ptrs[rank]).  workspace:
  * sharq_tp_transition_workspace_bytes(M/world) bytes of local scratch.
  * Requirements: M % (128*world) == 0, K % 128 == 0, K/32 <= 1024, 16-byte aligned buffers, the
  * same sequence of calls on every GPU.  Every cross-GPU wait is bounded (about ten seconds); one

@@ -33,6 +33,7 @@
 #include <cuda_bf16.h>
 
 #include <cstdint>
+#include <cstdlib>
 
 #include "prepare_device.cuh"
 #include "sp_transition.cuh"
@@ -69,6 +70,8 @@ struct SpParams {
   float *scale_out;                   // tensor scale, one float on this GPU
   uint8_t *a_comp, *e, *sfa_sparse, *q_res, *sf_res;  // this GPU's copy of the prepared activation (all m rows)
   long long mc_delta;                 // multicast address of that copy minus its local address
+  long long peer_delta[kSpMaxRanks];  // GPU r's copy as mapped here minus this GPU's copy (unicast all-gather)
+  int unicast;                        // all-gather by plain peer stores instead of multimem.st
   uint32_t *state[kSpMaxRanks];       // state[r]: GPU r's state words as mapped here
   int rank, world;
   int m, k;                           // whole activation
@@ -408,7 +411,10 @@ __global__ void __launch_bounds__(kThreads, 1) sp_transition_kernel(const SpPara
   }
 
   // ------------------------------------------------------------------ phase 3: push this GPU's rows to every GPU.
-  // A separate pass of contiguous 16-byte multicast stores: storing the packed words straight from the
+  // By default with plain peer stores to the other GPUs: a multicast store also comes back to its
+  // sender, so every GPU's port receives the whole packed activation, N / (N - 1) times the bytes
+  // that it needs (twice at two GPUs); SHARQ_TP_ALLGATHER=multicast selects multimem.st.
+  // A separate pass of contiguous 16-byte stores: storing the packed words straight from the
   // quantise phase (16 / 8 / 4-byte multimem.st as they are produced) was measured slower (82 against
   // 63 us per call at two GPUs): the switch wants a warp's multicast stores contiguous.
   grid_barrier(p, epoch, 2, true, 0x304);  // the packed rows are complete in this GPU's copy
@@ -439,7 +445,16 @@ __global__ void __launch_bounds__(kThreads, 1) sp_transition_kernel(const SpPara
         src = p.sf_res + (size_t)(p.row0 / 128) * (size_t)(k / 64) * 512 + j * 16;
       }
       const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(src));
-      st_multicast_16(src + p.mc_delta, v);
+      if (p.unicast) {
+        // one plain 16-byte store per peer, destinations staggered over the GPUs; a warp writes 512 contiguous bytes
+        for (int t = 1; t < p.world; ++t) {
+          int r = p.rank + t;
+          if (r >= p.world) r -= p.world;
+          *reinterpret_cast<uint4 *>(src + p.peer_delta[r]) = v;
+        }
+      } else {
+        st_multicast_16(src + p.mc_delta, v);
+      }
     }
   }
   // ---- C: this GPU's stores are out (grid barrier 3, CTA 0 alone waits), tell everyone, wait for everyone
@@ -498,6 +513,18 @@ cudaError_t run_sp_transition(const SpTransitionArgs &a, cudaStream_t stream) {
   p.q_res = static_cast<uint8_t *>(a.q_res);
   p.sf_res = static_cast<uint8_t *>(a.sf_res);
   p.mc_delta = a.multicast_delta;
+  {
+    static const bool multicast = [] {
+      const char *v = getenv("SHARQ_TP_ALLGATHER");  // tuning hook
+      return v != nullptr && v[0] == 'm';
+    }();
+    p.unicast = multicast ? 0 : 1;
+    // the state block lies in the same symmetric allocation as the output buffers, so the distance between
+    // two GPUs' mappings of it is the distance between their mappings of every byte of the allocation
+    for (int r = 0; r < a.world; ++r)
+      p.peer_delta[r] = (long long)(reinterpret_cast<intptr_t>(a.rank_state_ptrs[r]) -
+                                    reinterpret_cast<intptr_t>(a.rank_state_ptrs[a.rank]));
+  }
   for (int r = 0; r < a.world; ++r) p.state[r] = static_cast<uint32_t *>(a.rank_state_ptrs[r]);
   p.rank = a.rank;
   p.world = a.world;
