@@ -29,3 +29,27 @@ def test_bench_help_lists_modes():
     assert res.returncode == 0
     for flag in ("--gpus", "--steps", "--warmup", "--impl", "--shape-sweep", "--kernel-table", "--prefill-model"):
         assert flag in res.stdout
+
+
+def test_kernel_categories_follow_the_reference_profiler():
+    """bench.py --kernel-table sums kernels into the categories of the reference's prefill profiler
+    (benchmarks/e2e/profile_prefill_nvtx.py:159-275)."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("bench_module", ROOT / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    cat = bench.kernel_category
+    assert cat("void sharq::(anonymous namespace)::gemm_kernel<256, true, true, true, false>(CUtensorMap_st") == "gemm"
+    assert cat("sharq::(anonymous namespace)::gemm_grouped_kernel(sharq::(anonymous namespace)::GroupTable") == "gemm"
+    assert cat("nvjet_tst_128x8_64x12_2x1_v_bz_TNT") == "gemm"
+    assert cat("void sharq::(anonymous namespace)::prepare_fused_kernel<1, true, 512>(") == "sharq_kernel"
+    assert cat("void sharq::(anonymous namespace)::prepare_kernel<2, false, 2>(") == "sharq_kernel"
+    assert cat("void sharq::(anonymous namespace)::rms_stats_kernel<true>(") == "sharq_kernel"
+    assert cat("sharq::(anonymous namespace)::sp_transition_kernel(sharq::(anonymous namespace)::SpParams)") == "sharq_kernel+collective"
+    assert cat("void sharq::(anonymous namespace)::quantize_dense_nvfp4_kernel(") == "quantize_kernel"
+    assert cat("cudnn_generated_fort_native_sdpa_sm100_flash_fprop_f16_knob_7_128x128x128") == "attention"
+    assert cat("void sharq::(anonymous namespace)::add_rmsnorm_kernel<true>(") == "rmsnorm"
+    assert cat("ncclDevKernel_AllReduce_Sum_f32_RING_LL(ncclDevKernelArgsStorage<4096ul>)") == "collective"
+    assert cat("sharq::(anonymous namespace)::allreduce_multimem_kernel(") == "collective"
+    assert cat("sharq::(anonymous namespace)::rope_kernel(__nv_bfloat16*, long long") == "other"
