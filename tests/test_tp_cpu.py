@@ -213,3 +213,50 @@ def test_sequence_parallel_flow_equals_replicated_flow_gloo():
     assert not tp.SequenceParallelContext.supported(2048, 4096, 1)
     assert not tp.SequenceParallelContext.supported(2048 + 64, 4096, 8)
     assert tp.SequenceParallelContext.supported(2048, 4096, 8)
+
+
+@pytest.mark.parametrize("m,k,world", [(2048, 4096, 8), (2048, 4096, 2), (1024, 3584, 4), (512, 14336, 2), (256, 384, 2)])
+def test_transition_all_gather_ranges_cover_exactly_the_ranks_rows(m, k, world):
+    """The all-gather phase of the transition kernel (sp_transition.cu), restated: the 16-byte pieces a
+    rank pushes to its peers are enumerated as five contiguous runs (Q_res rows, A_comp rows, one run of
+    16-byte metadata rows per 256-column tile, the scale-factor bands of both layouts).  Together they
+    must be exactly the bytes that the rank's rows occupy in the reference layouts - every byte of
+    its rows, and no byte of another rank's rows."""
+    import numpy as np
+
+    from oracle import sharq_oracle as oracle
+
+    rows = m // world
+    assert rows % 128 == 0
+    aligned_m = (m + 127) // 128 * 128
+    groups32, groups_padded = k // 32, (k + 255) // 256 * 8
+    k_tiles = groups_padded // 8
+    for rank in range(world):
+        row0 = rank * rows
+        pieces = {name: set() for name in ("q_res", "a_comp", "e", "sfa", "sf_res")}
+        n_q, n_a, n_e = rows * (k // 2) // 16, rows * (k // 4) // 16, k_tiles * rows
+        n_sfa, n_sfr = (rows // 128) * (groups32 // 4) * 32, (rows // 128) * (k // 64) * 32
+        for i in range(n_q + n_a + n_e + n_sfa + n_sfr):  # the kernel's piece index -> (buffer, byte offset)
+            j = i
+            if j < n_q:
+                pieces["q_res"].add(row0 * (k // 2) + j * 16)
+            elif (j := j - n_q) < n_a:
+                pieces["a_comp"].add(row0 * (k // 4) + j * 16)
+            elif (j := j - n_a) < n_e:
+                kt, r = divmod(j, rows)
+                pieces["e"].add((kt * aligned_m + row0 + r) * 16)
+            elif (j := j - n_e) < n_sfa:
+                pieces["sfa"].add((row0 // 128) * (groups32 // 4) * 512 + j * 16)
+            else:
+                j -= n_sfa
+                pieces["sf_res"].add((row0 // 128) * (k // 64) * 512 + j * 16)
+        mine = np.arange(row0, row0 + rows)
+        want = {
+            "q_res": {int(r) * (k // 2) + c for r in mine for c in range(0, k // 2, 16)},
+            "a_comp": {int(r) * (k // 4) + c for r in mine for c in range(0, k // 4, 16)},
+            "e": {(kt * aligned_m + int(r)) * 16 for kt in range(k_tiles) for r in mine},
+            "sfa": {int(o) // 16 * 16 for o in oracle.sf_offsets(m, groups32)[mine].reshape(-1)},
+            "sf_res": {int(o) // 16 * 16 for o in oracle.sf_offsets(m, k // 16)[mine].reshape(-1)},
+        }
+        for name in pieces:
+            assert pieces[name] == want[name], (name, rank)
