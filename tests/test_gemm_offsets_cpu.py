@@ -99,3 +99,23 @@ def test_scatter_epilogue_stages_and_stores_every_piece_once(cols_per_warp):
                     cols = [p[1] for p in pieces[8 * q:8 * q + 8]]
                     assert len(rows) == 1 and cols == list(range(cols[0], cols[0] + 64, 8))
     assert len(stored) == 32 * (cols_per_warp // 8)
+
+
+@pytest.mark.parametrize("m,n,world", [(2048, 4096, 8), (2048, 4096, 2), (1024, 3584, 4), (256, 128, 2)])
+def test_scatter_epilogue_addresses_land_in_the_senders_block(m, n, world):
+    """Scatter mode of gemm.cu, restated: the 128-row tile m_tile belongs to GPU owner = m_tile * 128 / rows
+    (rows = M / world); its stores go to d_peer[owner] + (rank - owner) * rows * N + global_row * N + col, which
+    must be element (rank, global_row - owner * rows, col) of the owner's collection buffer [world][rows, N]."""
+    rows = m // world
+    assert rows % 128 == 0
+    for rank in range(world):
+        for m_tile in range(m // 128):
+            owner = (m_tile * 128) // rows
+            base = (rank - owner) * rows * n  # relative to d_peer[owner]
+            for grow in (m_tile * 128, m_tile * 128 + 127):
+                for col in (0, n - 8):
+                    off = base + grow * n + col
+                    local_row = grow - owner * rows
+                    assert 0 <= local_row < rows
+                    assert off == (rank * rows + local_row) * n + col
+                    assert 0 <= off < world * rows * n
